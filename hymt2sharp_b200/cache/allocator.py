@@ -29,9 +29,11 @@ class GroupSpec:
     head_dim: int
     planes: int             # layers (schedule entries) that store keys and values here
     window: int = 0         # for kind "window": positions that stay visible
+    streams: int = 2        # tensors per plane: 2 = keys and values; 1 = one vector per token that serves as both
+                            # (a compressed key/value row: kv_heads 1, head_dim its width)
 
     def key(self):
-        return (self.kind, self.kv_heads, self.head_dim, self.window)
+        return (self.kind, self.kv_heads, self.head_dim, self.window, self.streams)
 
 
 class FreeList:

@@ -1,8 +1,9 @@
 """Device side of the cache: the pools of key/value blocks of every group of
 layers, the block tables that kernels read, and the fixed-size state area.
 
-Storage of one group: [plane, 2 (keys, values), block, kv head, token in block,
-head_dim]; a plane is one layer's share.  `tables[g]` is an int32 device matrix
+Storage of one group: [plane, stream (keys, values; or the one vector of a group
+with a single stream), block, kv head, token in block, head_dim]; a plane is one
+layer's share.  `tables[g]` is an int32 device matrix
 [slot, logical block] → physical block (-1: none).  The host copy of the tables
 is the truth; rows that changed are sent before a step runs.
 
@@ -31,7 +32,7 @@ class PagedCache:
         self.num_blocks = -(-capacity_tokens // block_tokens)
         max_slots = max(1, min(max_slots, self.num_blocks))
         self.book = CacheBook(self.groups, self.num_blocks, block_tokens, max_slots)
-        self.storage = [torch.zeros((g.planes, 2, self.num_blocks, g.kv_heads, block_tokens, g.head_dim),
+        self.storage = [torch.zeros((g.planes, g.streams, self.num_blocks, g.kv_heads, block_tokens, g.head_dim),
                                     dtype=dtype, device=self.device) for g in self.groups]
         cols = self.num_blocks if max_sequence_tokens is None else -(-max_sequence_tokens // block_tokens)
         self.table_cols = max(1, min(cols, self.num_blocks))
@@ -54,11 +55,12 @@ class PagedCache:
 
     def bytes_per_token(self) -> int:
         es = torch.empty((), dtype=self.dtype).element_size()
-        return sum(2 * g.planes * g.kv_heads * g.head_dim * es for g in self.groups)
+        return sum(g.streams * g.planes * g.kv_heads * g.head_dim * es for g in self.groups)
 
-    def plane(self, group: int, plane: int) -> tuple[torch.Tensor, torch.Tensor]:
+    def plane(self, group: int, plane: int) -> tuple[torch.Tensor, torch.Tensor | None]:
+        """(keys, values) of a plane; a group with one stream has (vectors, None)."""
         s = self.storage[group]
-        return s[plane, 0], s[plane, 1]
+        return s[plane, 0], (s[plane, 1] if s.shape[1] > 1 else None)
 
     # -- growth -----------------------------------------------------------------
     def _grow(self, slots: int, cols: int) -> None:

@@ -91,6 +91,9 @@ def read_config_json(folder_or_file: str) -> dict:
 
 
 def architecture_name(data: dict, source: str = "config.json") -> str:
+    """The name that picks the model class: "architectures": [name], or "architecture": name."""
+    if "architectures" not in data and isinstance(data.get("architecture"), str):
+        return data["architecture"]
     archs = data.get("architectures")
     if not isinstance(archs, list) or len(archs) != 1 or not isinstance(archs[0], str):
         raise ConfigError(f"{source}: key 'architectures' must be a list with one architecture name")

@@ -44,5 +44,5 @@ def load_config(folder_or_file: str):
 
 
 def _load_builtin() -> None:
-    # the built-in architecture registers itself on import
-    from ..engine import hunyuan_dense  # noqa: F401
+    # the built-in architectures register themselves on import
+    from ..engine import hunyuan_dense, pemezen  # noqa: F401

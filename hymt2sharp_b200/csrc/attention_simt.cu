@@ -20,7 +20,7 @@
 
 namespace {
 
-constexpr int ROWS = 16, LANES_PER_ROW = 8, KEY_TILE = 32, MAX_D = 256;
+constexpr int ROWS = 16, LANES_PER_ROW = 8, KEY_TILE = 32, MAX_D = 256, MAX_D_WIDE = 640, MAX_DV_WIDE = 512;
 
 struct AttnParams {
     const void* q;        // [T, nh * d]
@@ -35,19 +35,23 @@ struct AttnParams {
     float* part_ml;         // [T, nh, splits, 2]
     int table_stride, block_tokens, nh, nkv, d, window, tokens_per_tile, heads_per_tile, head_chunks;
     int split_keys, max_splits;
+    int dv;                 // width of a value row and of an output row (d unless the values are narrower than the keys)
+    int v_from_k;           // the values are the first dv entries of the key rows (one vector per token serves as both)
     float scale;
     int* status;            // may be null; [0] = 2 when a row is longer than max_splits * split_keys covers
 };
 
-template <typename T>
+template <typename T, int NACC>
 __global__ void __launch_bounds__(ROWS* LANES_PER_ROW)
 attention_simt_kernel(AttnParams p) {
     extern __shared__ float smem[];
-    const int d = p.d;
+    const int d = p.d, dv = p.dv;
     float* Qs = smem;                          // [ROWS][d]
     float* Ks = Qs + ROWS * d;                 // [KEY_TILE][d + 1]
-    float* Vs = Ks + KEY_TILE * (d + 1);       // [KEY_TILE][d]
-    float* Ps = Vs + KEY_TILE * d;             // [ROWS][KEY_TILE]
+    float* Vs = Ks + KEY_TILE * (d + 1);       // [KEY_TILE][dv], or the key tile itself
+    float* Ps = Vs + (p.v_from_k ? 0 : KEY_TILE * dv);   // [ROWS][KEY_TILE]
+    const int v_ld = p.v_from_k ? d + 1 : dv;
+    if (p.v_from_k) Vs = Ks;
 
     const int b = blockIdx.z / p.max_splits, split = blockIdx.z % p.max_splits;
     const int slot = p.slot_ids[b];
@@ -87,9 +91,9 @@ attention_simt_kernel(AttnParams p) {
         Qs[i] = ok ? to_float(((const T*)p.q)[((size_t)(tok0 + tk) * p.nh + kvh * g + hg) * d + x]) : 0.f;
     }
 
-    float acc[MAX_D / LANES_PER_ROW];
+    float acc[NACC];
 #pragma unroll
-    for (int i = 0; i < MAX_D / LANES_PER_ROW; i++) acc[i] = 0.f;
+    for (int i = 0; i < NACC; i++) acc[i] = 0.f;
     float m = -INFINITY, l = 0.f;
 
     const int* table = p.block_table + (size_t)slot * p.table_stride;
@@ -99,13 +103,18 @@ attention_simt_kernel(AttnParams p) {
         const int block = table[k0 / p.block_tokens];
         const size_t base = (((size_t)block * p.nkv + kvh) * p.block_tokens + (k0 % p.block_tokens)) * d;
         const T* kp = (const T*)p.k_cache + base;
-        const T* vp = (const T*)p.v_cache + base;
         const int valid = min(KEY_TILE, kv_len - k0);
         for (int i = tid; i < KEY_TILE * d; i += blockDim.x) {
             const int j = i / d, x = i - j * d;
             const bool ok = j < valid && block >= 0;
             Ks[j * (d + 1) + x] = ok ? to_float(kp[i]) : 0.f;
-            Vs[i] = ok ? to_float(vp[i]) : 0.f;
+        }
+        if (!p.v_from_k) {
+            const T* vp = (const T*)p.v_cache + (((size_t)block * p.nkv + kvh) * p.block_tokens + (k0 % p.block_tokens)) * dv;
+            for (int i = tid; i < KEY_TILE * dv; i += blockDim.x) {
+                const bool ok = i / dv < valid && block >= 0;
+                Vs[i] = ok ? to_float(vp[i]) : 0.f;
+            }
         }
         __syncthreads();
 
@@ -144,11 +153,11 @@ attention_simt_kernel(AttnParams p) {
         m = m_new;
         __syncwarp();
 #pragma unroll
-        for (int i = 0; i < MAX_D / LANES_PER_ROW; i++) {
+        for (int i = 0; i < NACC; i++) {
             const int x = c + i * LANES_PER_ROW;
-            if (x < d) {
+            if (x < dv) {
                 float a = acc[i] * corr;
-                for (int j = 0; j < KEY_TILE; j++) a = fmaf(Ps[r * KEY_TILE + j], Vs[j * d + x], a);
+                for (int j = 0; j < KEY_TILE; j++) a = fmaf(Ps[r * KEY_TILE + j], Vs[j * v_ld + x], a);
                 acc[i] = a;
             }
         }
@@ -157,11 +166,11 @@ attention_simt_kernel(AttnParams p) {
     if (!row_ok) return;
     const size_t row_index = (size_t)(tok0 + row_tok) * p.nh + head;
     if (p.split_keys > 0) {
-        float* pa = p.part_acc + (row_index * p.max_splits + split) * d;
+        float* pa = p.part_acc + (row_index * p.max_splits + split) * dv;
 #pragma unroll
-        for (int i = 0; i < MAX_D / LANES_PER_ROW; i++) {
+        for (int i = 0; i < NACC; i++) {
             const int x = c + i * LANES_PER_ROW;
-            if (x < d) pa[x] = acc[i];
+            if (x < dv) pa[x] = acc[i];
         }
         if (c == 0) {
             float* ml = p.part_ml + (row_index * p.max_splits + split) * 2;
@@ -170,11 +179,11 @@ attention_simt_kernel(AttnParams p) {
         }
     } else {
         const float inv = l > 0.f ? 1.0f / l : 0.f;
-        T* o = (T*)p.out + row_index * d;
+        T* o = (T*)p.out + row_index * dv;
 #pragma unroll
-        for (int i = 0; i < MAX_D / LANES_PER_ROW; i++) {
+        for (int i = 0; i < NACC; i++) {
             const int x = c + i * LANES_PER_ROW;
-            if (x < d) o[x] = from_float<T>(acc[i] * inv);
+            if (x < dv) o[x] = from_float<T>(acc[i] * inv);
         }
     }
 }
@@ -205,11 +214,11 @@ __global__ void attention_merge_kernel(AttnParams p, int total_tokens) {
     float L = 0.f;
     for (int s = s_begin; s < s_end; s++) L += ml[2 * s + 1] * expf(ml[2 * s] - M);
     const float inv = L > 0.f ? 1.0f / L : 0.f;
-    const float* pa = p.part_acc + (size_t)row * p.max_splits * p.d;
-    for (int x = threadIdx.x; x < p.d; x += blockDim.x) {
+    const float* pa = p.part_acc + (size_t)row * p.max_splits * p.dv;
+    for (int x = threadIdx.x; x < p.dv; x += blockDim.x) {
         float a = 0.f;
-        for (int s = s_begin; s < s_end; s++) a = fmaf(pa[(size_t)s * p.d + x], expf(ml[2 * s] - M), a);
-        ((T*)p.out)[(size_t)row * p.d + x] = from_float<T>(a * inv);
+        for (int s = s_begin; s < s_end; s++) a = fmaf(pa[(size_t)s * p.dv + x], expf(ml[2 * s] - M), a);
+        ((T*)p.out)[(size_t)row * p.dv + x] = from_float<T>(a * inv);
     }
 }
 
@@ -223,7 +232,7 @@ int hymt2_attention_merge_launch(void* out, int dtype, const int* cu_seqlens, co
     AttnParams p{};
     p.status = status;
     p.out = out; p.cu_seqlens = cu_seqlens; p.slot_ids = slot_ids; p.kv_lens = kv_lens;
-    p.part_acc = part_acc; p.part_ml = part_ml; p.nh = nh; p.d = d; p.window = window;
+    p.part_acc = part_acc; p.part_ml = part_ml; p.nh = nh; p.d = d; p.dv = d; p.window = window;
     p.split_keys = split_keys; p.max_splits = max_splits;
     HYMT2_DISPATCH_DTYPE(dtype, T, (attention_merge_kernel<T><<<tokens * nh, 64, 0, stream>>>(p, tokens)));
     return hymt2_check_launch("attention_merge");
@@ -236,16 +245,19 @@ HYMT2_API int hymt2_attention_simt_scratch(int tokens, int nh, int d, int max_sp
     return HYMT2_OK;
 }
 
-HYMT2_API int hymt2_attention_simt(void* out, const void* q, const void* k_cache, const void* v_cache, int dtype,
-                                   const int* block_table, int table_stride, int block_tokens,
-                                   const int* cu_seqlens, const int* slot_ids, const int* kv_lens,
-                                   int batch, int tokens, int max_new_tokens, int nh, int nkv, int d,
-                                   float scale, int window, int split_keys, int max_splits,
-                                   float* part_acc, float* part_ml, cudaStream_t stream, int* status) {
+// The general form: keys of width d, values of width dv (v_cache null: the values are the first dv entries of
+// the key rows).  q is [T, nh * d], out [T, nh * dv], the partials [T, nh, splits, dv].
+static int attention_simt_general(void* out, const void* q, const void* k_cache, const void* v_cache, int dtype,
+                                  const int* block_table, int table_stride, int block_tokens,
+                                  const int* cu_seqlens, const int* slot_ids, const int* kv_lens,
+                                  int batch, int tokens, int max_new_tokens, int nh, int nkv, int d, int dv,
+                                  float scale, int window, int split_keys, int max_splits,
+                                  float* part_acc, float* part_ml, cudaStream_t stream, int* status) {
     if (tokens == 0 || batch == 0) return HYMT2_OK;
     HYMT2_REQUIRE(batch > 0 && tokens > 0 && nh > 0 && nkv > 0, "attention: bad sizes");
     HYMT2_REQUIRE(nh % nkv == 0, "attention: %d heads are not a multiple of %d kv heads", nh, nkv);
-    HYMT2_REQUIRE(d > 0 && d % 8 == 0 && d <= MAX_D, "attention: head_dim %d must be a multiple of 8, at most %d", d, MAX_D);
+    HYMT2_REQUIRE(d > 0 && d <= MAX_D_WIDE && dv > 0 && dv <= MAX_DV_WIDE && (v_cache || dv <= d),
+                  "attention: keys of %d and values of %d entries are not taken (at most %d and %d)", d, dv, MAX_D_WIDE, MAX_DV_WIDE);
     HYMT2_REQUIRE(block_tokens % KEY_TILE == 0, "attention: block_tokens %d must be a multiple of %d", block_tokens, KEY_TILE);
     HYMT2_REQUIRE(split_keys == 0 || (split_keys % KEY_TILE == 0 && max_splits > 0 && part_acc && part_ml),
                   "attention: split_keys %d must be a multiple of %d and comes with scratch", split_keys, KEY_TILE);
@@ -255,6 +267,7 @@ HYMT2_API int hymt2_attention_simt(void* out, const void* q, const void* k_cache
     p.cu_seqlens = cu_seqlens; p.slot_ids = slot_ids; p.kv_lens = kv_lens;
     p.part_acc = part_acc; p.part_ml = part_ml;
     p.table_stride = table_stride; p.block_tokens = block_tokens; p.nh = nh; p.nkv = nkv; p.d = d;
+    p.dv = dv; p.v_from_k = v_cache ? 0 : 1;
     p.window = window;
     p.heads_per_tile = g < ROWS ? g : ROWS;
     p.tokens_per_tile = ROWS / p.heads_per_tile;
@@ -263,16 +276,17 @@ HYMT2_API int hymt2_attention_simt(void* out, const void* q, const void* k_cache
     p.split_keys = split_keys; p.max_splits = split_keys > 0 ? max_splits : 1;
     p.scale = scale;
     p.status = status;
-    const size_t smem = sizeof(float) * ((size_t)ROWS * d + (size_t)KEY_TILE * (d + 1) + (size_t)KEY_TILE * d + ROWS * KEY_TILE);
+    const size_t smem = sizeof(float) * ((size_t)ROWS * d + (size_t)KEY_TILE * (d + 1) + (v_cache ? (size_t)KEY_TILE * dv : 0) + ROWS * KEY_TILE);
     dim3 grid((max_new_tokens + p.tokens_per_tile - 1) / p.tokens_per_tile, nkv * p.head_chunks, batch * p.max_splits);
     HYMT2_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "attention: grid too large (batch %d x splits %d)", batch, p.max_splits);
     int rc = HYMT2_OK;
     HYMT2_DISPATCH_DTYPE(dtype, T, {
+        auto kernel = dv <= MAX_D ? attention_simt_kernel<T, MAX_D / LANES_PER_ROW> : attention_simt_kernel<T, MAX_DV_WIDE / LANES_PER_ROW>;
         if (smem > 48 * 1024) {
-            cudaError_t e = cudaFuncSetAttribute(attention_simt_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) { hymt2_set_error("attention: %s", cudaGetErrorString(e)); return HYMT2_ERR_LAUNCH; }
         }
-        attention_simt_kernel<T><<<grid, ROWS * LANES_PER_ROW, smem, stream>>>(p);
+        kernel<<<grid, ROWS * LANES_PER_ROW, smem, stream>>>(p);
         rc = hymt2_check_launch("attention_simt");
         if (rc == HYMT2_OK && split_keys > 0) {
             attention_merge_kernel<T><<<tokens * nh, 64, 0, stream>>>(p, tokens);
@@ -280,6 +294,33 @@ HYMT2_API int hymt2_attention_simt(void* out, const void* q, const void* k_cache
         }
     });
     return rc;
+}
+
+HYMT2_API int hymt2_attention_simt(void* out, const void* q, const void* k_cache, const void* v_cache, int dtype,
+                                   const int* block_table, int table_stride, int block_tokens,
+                                   const int* cu_seqlens, const int* slot_ids, const int* kv_lens,
+                                   int batch, int tokens, int max_new_tokens, int nh, int nkv, int d,
+                                   float scale, int window, int split_keys, int max_splits,
+                                   float* part_acc, float* part_ml, cudaStream_t stream, int* status) {
+    HYMT2_REQUIRE(d > 0 && d % 8 == 0 && d <= MAX_D, "attention: head_dim %d must be a multiple of 8, at most %d", d, MAX_D);
+    HYMT2_REQUIRE(v_cache != nullptr, "attention: no values");
+    return attention_simt_general(out, q, k_cache, v_cache, dtype, block_table, table_stride, block_tokens, cu_seqlens, slot_ids,
+                                  kv_lens, batch, tokens, max_new_tokens, nh, nkv, d, d, scale, window, split_keys, max_splits,
+                                  part_acc, part_ml, stream, status);
+}
+
+// Attention over a cache that holds ONE vector per token and layer, shared by all heads: the key of every head
+// is the whole vector (width d), its value the first dv entries.  (A low-rank key/value cache read in its
+// compressed form: the queries come already multiplied into the compressed space.)
+HYMT2_API int hymt2_attention_shared_vector(void* out, const void* q, const void* cache, int dtype,
+                                            const int* block_table, int table_stride, int block_tokens,
+                                            const int* cu_seqlens, const int* slot_ids, const int* kv_lens,
+                                            int batch, int tokens, int max_new_tokens, int nh, int d, int dv,
+                                            float scale, int window, int split_keys, int max_splits,
+                                            float* part_acc, float* part_ml, cudaStream_t stream, int* status) {
+    return attention_simt_general(out, q, cache, nullptr, dtype, block_table, table_stride, block_tokens, cu_seqlens, slot_ids,
+                                  kv_lens, batch, tokens, max_new_tokens, nh, 1, d, dv, scale, window, split_keys, max_splits,
+                                  part_acc, part_ml, stream, status);
 }
 
 // ---------------------------------------------------------------------------

@@ -1,0 +1,92 @@
+// Small element-by-element steps between the products of a layer.  All arithmetic is float32; the rows may be
+// views into wider buffers (a leading dimension comes with every matrix).
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ float softplus_e(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+    return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+// x[r, c] <- act(x[r, c] + bias[c]); the first `act_cols` columns get the tanh form of GELU, the others the bias alone.
+template <typename T>
+__global__ void bias_act_kernel(T* __restrict__ x, const float* __restrict__ bias, int cols, long ld, int act_cols, size_t total) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const size_t r = i / cols;
+    const int c = (int)(i - r * cols);
+    T* px = x + r * ld + c;
+    float v = to_float(*px) + (bias ? bias[c] : 0.f);
+    if (c < act_cols) v = gelu_tanh_f(v);
+    *px = from_float<T>(v);
+}
+
+// xIELU with its two numbers (p, q) read from the device: for z > 0  softplus(p) z^2 + z / 2;
+// for z <= 0  (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2.
+template <typename T>
+__global__ void xielu_kernel(T* __restrict__ out, const T* __restrict__ x, const float* __restrict__ pq, size_t total) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const float ap = softplus_e(pq[0]), an = 0.5f + softplus_e(pq[1]);
+    const float z = to_float(x[i]);
+    const float v = z > 0.f ? fmaf(ap * z, z, 0.5f * z) : fmaf(an, expm1f(z) - z, 0.5f * z);
+    out[i] = from_float<T>(v);
+}
+
+// x[t, h, v] <- x[t, h, v] * sigmoid(g[t, per_head ? h : h * vdim + v])
+template <typename T>
+__global__ void sigmoid_gate_kernel(T* __restrict__ x, const T* __restrict__ g, int heads, int vdim, long ldg, int per_head,
+                                    size_t total) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const int width = heads * vdim;
+    const size_t t = i / width;
+    const int c = (int)(i - t * width);
+    const float gate = to_float(g[t * ldg + (per_head ? c / vdim : c)]);
+    x[i] = from_float<T>(to_float(x[i]) / (1.0f + expf(-gate)));
+}
+
+// x <- cap * tanh(x / cap)
+__global__ void softcap_kernel(float* __restrict__ x, float cap, size_t total) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    x[i] = cap * tanhf(x[i] / cap);
+}
+
+inline unsigned blocks_for(size_t total) { return (unsigned)((total + 255) / 256); }
+
+}  // namespace
+
+HYMT2_API int hymt2_bias_act(void* x, int dtype, const float* bias, int rows, int cols, long ld, int act_cols, cudaStream_t stream) {
+    if (rows == 0 || cols == 0) return HYMT2_OK;
+    HYMT2_REQUIRE(rows > 0 && cols > 0 && ld >= cols && act_cols >= 0 && act_cols <= cols, "bias_act: bad sizes");
+    const size_t total = (size_t)rows * cols;
+    HYMT2_DISPATCH_DTYPE(dtype, T, (bias_act_kernel<T><<<blocks_for(total), 256, 0, stream>>>((T*)x, bias, cols, ld, act_cols, total)));
+    return hymt2_check_launch("bias_act");
+}
+
+HYMT2_API int hymt2_xielu(void* out, const void* x, int dtype, const float* pq, long total, cudaStream_t stream) {
+    if (total == 0) return HYMT2_OK;
+    HYMT2_REQUIRE(total > 0 && pq != nullptr, "xielu: bad sizes");
+    HYMT2_DISPATCH_DTYPE(dtype, T, (xielu_kernel<T><<<blocks_for((size_t)total), 256, 0, stream>>>((T*)out, (const T*)x, pq, (size_t)total)));
+    return hymt2_check_launch("xielu");
+}
+
+HYMT2_API int hymt2_sigmoid_gate(void* x, const void* g, int dtype, int rows, int heads, int vdim, long ldg, int per_head,
+                                 cudaStream_t stream) {
+    if (rows == 0) return HYMT2_OK;
+    HYMT2_REQUIRE(rows > 0 && heads > 0 && vdim > 0, "sigmoid_gate: bad sizes");
+    const size_t total = (size_t)rows * heads * vdim;
+    HYMT2_DISPATCH_DTYPE(dtype, T, (sigmoid_gate_kernel<T><<<blocks_for(total), 256, 0, stream>>>((T*)x, (const T*)g, heads, vdim, ldg,
+                                                                                               per_head, total)));
+    return hymt2_check_launch("sigmoid_gate");
+}
+
+HYMT2_API int hymt2_softcap(float* x, float cap, long total, cudaStream_t stream) {
+    if (total == 0) return HYMT2_OK;
+    HYMT2_REQUIRE(total > 0 && cap > 0.f, "softcap: bad arguments");
+    softcap_kernel<<<blocks_for((size_t)total), 256, 0, stream>>>(x, cap, (size_t)total);
+    return hymt2_check_launch("softcap");
+}

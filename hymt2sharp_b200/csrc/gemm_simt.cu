@@ -39,8 +39,12 @@ __device__ __forceinline__ void load4(const T* row, int k, int K, bool row_ok, b
 template <typename TA, typename TW, typename TC, int EPI>
 __global__ void __launch_bounds__(THREADS)
 gemm_simt_kernel(TC* __restrict__ C, const TA* __restrict__ A, const TW* __restrict__ W, int M, int N, int K,
-                 long lda, long ldw, long ldc, bool vec_a, bool vec_w) {
+                 long lda, long ldw, long ldc, bool vec_a, bool vec_w, long a_bs, long w_bs, long c_bs) {
     constexpr int NB = EPI == EPI_SWIGLU ? 2 : 1;
+    // a batch of products with the same sizes: blockIdx.z picks the operands (strides in elements)
+    A += (size_t)blockIdx.z * a_bs;
+    W += (size_t)blockIdx.z * w_bs;
+    C += (size_t)blockIdx.z * c_bs;
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[NB][BK][BN + 4];
     const int tid = threadIdx.x;
@@ -116,13 +120,13 @@ gemm_simt_kernel(TC* __restrict__ C, const TA* __restrict__ A, const TW* __restr
 
 template <typename TA, typename TW, typename TC>
 int launch(void* C, const void* A, const void* W, int M, int N, int K, long lda, long ldw, long ldc, int epi,
-           cudaStream_t stream) {
-    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-    const bool vec_a = (lda % 4 == 0) && ((uintptr_t)A % 16 == 0);
-    const bool vec_w = (ldw % 4 == 0) && ((uintptr_t)W % 16 == 0);
+           cudaStream_t stream, int batch = 1, long a_bs = 0, long w_bs = 0, long c_bs = 0) {
+    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, batch);
+    const bool vec_a = (lda % 4 == 0) && ((uintptr_t)A % 16 == 0) && (a_bs * sizeof(TA)) % 16 == 0;
+    const bool vec_w = (ldw % 4 == 0) && ((uintptr_t)W % 16 == 0) && (w_bs * sizeof(TW)) % 16 == 0;
 #define HYMT2_GEMM_CASE(E)                                                                                  \
     gemm_simt_kernel<TA, TW, TC, E><<<grid, THREADS, 0, stream>>>((TC*)C, (const TA*)A, (const TW*)W, M, N, K, \
-                                                                  lda, ldw, ldc, vec_a, vec_w)
+                                                                  lda, ldw, ldc, vec_a, vec_w, a_bs, w_bs, c_bs)
     if (epi == EPI_STORE) HYMT2_GEMM_CASE(EPI_STORE);
     else if (epi == EPI_ACCUMULATE) HYMT2_GEMM_CASE(EPI_ACCUMULATE);
     else HYMT2_GEMM_CASE(EPI_SWIGLU);
@@ -143,5 +147,21 @@ HYMT2_API int hymt2_gemm_simt(void* C, int c_dtype, const void* A, int a_dtype, 
     HYMT2_REQUIRE((M + BM - 1) / BM <= 65535, "gemm: M=%d needs more than 65535 row tiles", M);
     HYMT2_DISPATCH_DTYPE(a_dtype, TA, HYMT2_DISPATCH_DTYPE(w_dtype, TW, HYMT2_DISPATCH_DTYPE(c_dtype, TC,
         return (launch<TA, TW, TC>(C, A, W, M, N, K, lda, ldw, ldc, epilogue, stream)))));
+    return HYMT2_OK;
+}
+
+// `batch` products of the same sizes in one launch: product z reads A + z * a_bs and W + z * w_bs and writes
+// C + z * c_bs (strides in elements).  Per-head and per-block matrices (a block-diagonal gate, a projection that
+// every head has of its own) are batches of this kind.
+HYMT2_API int hymt2_gemm_simt_batched(void* C, int c_dtype, const void* A, int a_dtype, const void* W, int w_dtype,
+                                      int M, int N, int K, long lda, long ldw, long ldc, int batch, long a_bs,
+                                      long w_bs, long c_bs, int epilogue, cudaStream_t stream) {
+    if (M == 0 || N == 0 || batch == 0) return HYMT2_OK;
+    HYMT2_REQUIRE(M > 0 && N > 0 && K > 0 && batch > 0 && batch <= 65535, "gemm: bad sizes M=%d N=%d K=%d batch=%d", M, N, K, batch);
+    HYMT2_REQUIRE(epilogue >= 0 && epilogue <= 1, "gemm: a batch takes the store and accumulate epilogues, not %d", epilogue);
+    HYMT2_REQUIRE(lda >= K && ldw >= K && ldc >= N, "gemm: a leading dimension is smaller than its row");
+    HYMT2_REQUIRE((M + BM - 1) / BM <= 65535, "gemm: M=%d needs more than 65535 row tiles", M);
+    HYMT2_DISPATCH_DTYPE(a_dtype, TA, HYMT2_DISPATCH_DTYPE(w_dtype, TW, HYMT2_DISPATCH_DTYPE(c_dtype, TC,
+        return (launch<TA, TW, TC>(C, A, W, M, N, K, lda, ldw, ldc, epilogue, stream, batch, a_bs, w_bs, c_bs)))));
     return HYMT2_OK;
 }

@@ -76,6 +76,55 @@ HYMT2_API int hymt2_rmsnorm(void* y, int y_dtype, const void* x, int x_dtype, co
     return hymt2_check_launch("rmsnorm");
 }
 
+// RMSNorm in groups: a row is cut into `groups` equal consecutive parts, each part is divided by its own
+// sqrt(mean(part^2) + eps), and the whole is multiplied by the gain; all in float32.  One block per (row, part).
+// `ADD`: the result is added to y (float32 rows that already hold something: a residual stream that takes a
+// sublayer's output after a norm) instead of stored.
+template <typename TX, typename TW, typename TY, bool ADD>
+__global__ void rmsnorm_groups_kernel(TY* __restrict__ y, const TX* __restrict__ x, const TW* __restrict__ gain,
+                                      const int* __restrict__ rows_index, int dim, int part, float eps, float out_scale) {
+    __shared__ float scratch[33];
+    const int r = blockIdx.x, g = blockIdx.y;
+    const TX* src = x + (size_t)(rows_index ? rows_index[r] : r) * dim + (size_t)g * part;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < part; i += blockDim.x) {
+        float v = to_float(src[i]);
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss / (float)part + eps);
+    TY* dst = y + (size_t)r * dim + (size_t)g * part;
+    const TW* gn = gain + (size_t)g * part;
+    for (int i = threadIdx.x; i < part; i += blockDim.x) {
+        float v = to_float(src[i]) * scale * to_float(gn[i]);
+        if (out_scale != 1.0f) v *= out_scale;
+        if constexpr (ADD) dst[i] = from_float<TY>(to_float(dst[i]) + v);
+        else dst[i] = from_float<TY>(v);
+    }
+}
+
+HYMT2_API int hymt2_rmsnorm_groups(void* y, int y_dtype, const void* x, int x_dtype, const void* gain, int gain_dtype,
+                                   const int* rows_index, int rows, int dim, int groups, float eps, float out_scale,
+                                   int add, cudaStream_t stream) {
+    if (rows == 0) return HYMT2_OK;
+    HYMT2_REQUIRE(rows > 0 && dim > 0 && groups > 0 && dim % groups == 0 && groups <= 65535,
+                  "rmsnorm: bad sizes rows=%d dim=%d groups=%d", rows, dim, groups);
+    HYMT2_REQUIRE(!add || y_dtype == HYMT2_F32, "rmsnorm: adding into the output needs float32 rows");
+    const int part = dim / groups;
+    const int threads = part >= 1024 ? 256 : (part >= 256 ? 128 : (part >= 64 ? 64 : 32));
+    const dim3 grid(rows, groups);
+    HYMT2_DISPATCH_DTYPE(x_dtype, TX, HYMT2_DISPATCH_DTYPE(gain_dtype, TW, {
+        if (add) {
+            rmsnorm_groups_kernel<TX, TW, float, true><<<grid, threads, 0, stream>>>((float*)y, (const TX*)x, (const TW*)gain,
+                                                                                    rows_index, dim, part, eps, out_scale);
+        } else {
+            HYMT2_DISPATCH_DTYPE(y_dtype, TY, (rmsnorm_groups_kernel<TX, TW, TY, false><<<grid, threads, 0, stream>>>(
+                (TY*)y, (const TX*)x, (const TW*)gain, rows_index, dim, part, eps, out_scale)));
+        }
+    }));
+    return hymt2_check_launch("rmsnorm_groups");
+}
+
 // a = gate / (1 + exp(-gate)) * up on a [rows, 2*width] input whose first half of every row is
 // the gate and whose second half is the up projection (src/HyMT2Sharp/Ops.cs:999-1055).
 template <typename T>

@@ -1,0 +1,208 @@
+// Parts of a layer that carry a small state from token to token: a short causal convolution over time on each
+// channel, and the real-gated linear recurrence of a recurrent block.  Both run over the packed tokens of a step
+// (sequence b brings the tokens cu_seqlens[b]..cu_seqlens[b+1]-1, the first of them at position kv_lens[b] - n_b)
+// and keep their state in the per-sequence state rows of the cache (state + slot * state_stride bytes).
+// A sequence whose step starts at position 0 starts from zeros whatever its state row holds.
+#include "common.cuh"
+
+namespace {
+
+constexpr int CONV_MAX_TAPS = 16, CONV_CHUNK = 32, CONV_THREADS = 128;
+
+struct ConvParams {
+    const void* x;        // [T, ldx] the inputs (channel c of token t at x[t * ldx + c])
+    void* out;            // [T, ldo]; must not overlap x
+    const float* w;       // [C, taps]; w[c][taps - 1] multiplies the current token
+    const float* bias;    // [C] or null
+    uint8_t* state;       // state rows; this convolution's part holds float32 [taps - 1][C], oldest first
+    long state_stride;    // bytes between two slots' rows
+    const int* cu_seqlens;
+    const int* slot_ids;
+    const int* kv_lens;
+    int channels, taps, ldx, ldo, add_input;
+};
+
+// out_t = (add_input ? x_t : 0) + bias + sum_j w[:, j] * x_(t - taps + 1 + j), zeros before the sequence's start.
+// One thread owns a channel over a chunk of a sequence's new tokens and slides a window of registers over it.  The
+// thread of the first chunk is the only one that reads the state (for the inputs before this step) and, once it has,
+// writes the new one: the last taps - 1 inputs of (old state, new tokens).
+template <typename T>
+__global__ void __launch_bounds__(CONV_THREADS)
+causal_conv_kernel(ConvParams p) {
+    const int c = blockIdx.x * CONV_THREADS + threadIdx.x;
+    const int b = blockIdx.z;
+    if (c >= p.channels) return;
+    const int tok0 = p.cu_seqlens[b], n = p.cu_seqlens[b + 1] - tok0;
+    const int i0 = blockIdx.y * CONV_CHUNK;
+    if (i0 >= n) return;
+    const int slot = p.slot_ids[b];
+    const T* x = (const T*)p.x + (size_t)tok0 * p.ldx + c;
+    T* out = (T*)p.out + (size_t)tok0 * p.ldo + c;
+    const int i1 = min(n, i0 + CONV_CHUNK);
+    if (slot < 0) {   // a padding row: nothing is remembered, the output is defined
+        for (int i = i0; i < i1; i++) out[(size_t)i * p.ldo] = from_float<T>(0.f);
+        return;
+    }
+    const int start = p.kv_lens[b] - n;   // position of the step's first token
+    const int taps = p.taps, hist = taps - 1;
+    float* st = (float*)(p.state + (size_t)slot * p.state_stride) + c;   // st[j * channels], j = 0 oldest
+    float w[CONV_MAX_TAPS], win[CONV_MAX_TAPS];
+#pragma unroll
+    for (int j = 0; j < CONV_MAX_TAPS; j++) w[j] = j < taps ? p.w[(size_t)c * taps + j] : 0.f;
+    // win[j] for j < hist: the input at index i0 - hist + j among the new tokens
+#pragma unroll
+    for (int j = 0; j < CONV_MAX_TAPS; j++) {
+        win[j] = 0.f;
+        if (j < hist) {
+            const int idx = i0 - hist + j;
+            if (idx >= 0) win[j] = to_float(x[(size_t)idx * p.ldx]);
+            else if (start + idx >= 0) win[j] = st[(size_t)(hist + idx) * p.channels];
+        }
+    }
+    const float bias = p.bias ? p.bias[c] : 0.f;
+    for (int i = i0; i < i1; i++) {
+        const float cur = to_float(x[(size_t)i * p.ldx]);
+        float acc = 0.f;
+#pragma unroll
+        for (int j = 0; j < CONV_MAX_TAPS; j++)
+            if (j < hist) acc = fmaf(w[j], win[j], acc);
+        acc = fmaf(w[hist], cur, acc) + bias;
+        if (p.add_input) acc += cur;
+        out[(size_t)i * p.ldo] = from_float<T>(acc);
+#pragma unroll
+        for (int j = 0; j < CONV_MAX_TAPS - 1; j++)
+            if (j + 1 < hist) win[j] = win[j + 1];
+        if (hist > 0) {
+#pragma unroll
+            for (int j = 0; j < CONV_MAX_TAPS; j++)
+                if (j == hist - 1) win[j] = cur;
+        }
+    }
+    if (i0 == 0) {
+        // new[j] = combined[n + j] of combined = (old state, new tokens); ascending j reads only what is not yet overwritten
+        for (int j = 0; j < hist; j++) {
+            const int idx = n - hist + j;   // among the new tokens
+            float v = 0.f;
+            if (idx >= 0) v = to_float(x[(size_t)idx * p.ldx]);
+            else if (start + idx >= 0) v = st[(size_t)(hist + idx) * p.channels];
+            st[(size_t)j * p.channels] = v;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// The real-gated linear recurrence.  Per channel c and token t, everything in float32:
+//   r = sigmoid(gr + br[c]), i = sigmoid(gi + bi[c])        gr, gi: the gates' sums before their biases
+//   log a = -decay * r * softplus(lam[c]);  a = exp(log a)
+//   S <- a * S + sqrt(1 - a^2) * i * u;   out = S * y
+// One thread owns a channel of one sequence and walks its new tokens in order; the values of RG_BATCH tokens are
+// loaded and their coefficients computed side by side, then chained.
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int RG_BATCH = 8, RG_THREADS = 64;
+
+struct ScanParams {
+    const float* gates;   // [T, 2 * width]: gr then gi of every token
+    const void* u;        // [T, ldu]
+    const void* y;        // [T, ldy]
+    void* out;            // [T, ldo]
+    const float* br;      // [width]
+    const float* bi;      // [width]
+    const float* lam;     // [width]
+    uint8_t* state;
+    long state_stride;
+    const int* cu_seqlens;
+    const int* slot_ids;
+    const int* kv_lens;
+    int width, ldu, ldy, ldo;
+    float decay;
+};
+
+__device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+template <typename T>
+__global__ void __launch_bounds__(RG_THREADS)
+rglru_scan_kernel(ScanParams p) {
+    const int c = blockIdx.x * RG_THREADS + threadIdx.x;
+    const int b = blockIdx.y;
+    if (c >= p.width) return;
+    const int tok0 = p.cu_seqlens[b], n = p.cu_seqlens[b + 1] - tok0;
+    const int slot = p.slot_ids[b];
+    T* out = (T*)p.out + (size_t)tok0 * p.ldo + c;
+    if (slot < 0) {
+        for (int i = 0; i < n; i++) out[(size_t)i * p.ldo] = from_float<T>(0.f);
+        return;
+    }
+    const int start = p.kv_lens[b] - n;
+    float* st = (float*)(p.state + (size_t)slot * p.state_stride) + c;
+    float S = start > 0 ? *st : 0.f;
+    const float br = p.br[c], bi = p.bi[c];
+    const float rate = -p.decay * softplus_f(p.lam[c]);
+    const float* gates = p.gates + (size_t)tok0 * 2 * p.width + c;
+    const T* u = (const T*)p.u + (size_t)tok0 * p.ldu + c;
+    const T* y = (const T*)p.y + (size_t)tok0 * p.ldy + c;
+    for (int i0 = 0; i0 < n; i0 += RG_BATCH) {
+        float a[RG_BATCH], bx[RG_BATCH], yy[RG_BATCH];
+#pragma unroll
+        for (int k = 0; k < RG_BATCH; k++) {
+            const int i = i0 + k;
+            a[k] = 1.f; bx[k] = 0.f; yy[k] = 0.f;
+            if (i < n) {
+                const float r = sigmoid_f(gates[(size_t)i * 2 * p.width] + br);
+                const float g = sigmoid_f(gates[(size_t)i * 2 * p.width + p.width] + bi);
+                const float log_a = rate * r;
+                a[k] = expf(log_a);
+                bx[k] = sqrtf(-expm1f(2.f * log_a)) * g * to_float(u[(size_t)i * p.ldu]);
+                yy[k] = to_float(y[(size_t)i * p.ldy]);
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < RG_BATCH; k++) {
+            const int i = i0 + k;
+            if (i < n) {
+                S = fmaf(a[k], S, bx[k]);
+                out[(size_t)i * p.ldo] = from_float<T>(S * yy[k]);
+            }
+        }
+    }
+    *st = S;
+}
+
+}  // namespace
+
+HYMT2_API int hymt2_causal_conv(void* out, const void* x, int dtype, const float* w, const float* bias, void* state,
+                                long state_offset, long state_stride, const int* cu_seqlens, const int* slot_ids,
+                                const int* kv_lens, int batch, int max_new_tokens, int channels, int taps, int ldx, int ldo,
+                                int add_input, cudaStream_t stream) {
+    if (batch == 0 || max_new_tokens == 0) return HYMT2_OK;
+    HYMT2_REQUIRE(batch > 0 && batch <= 65535 && channels > 0 && max_new_tokens > 0, "causal_conv: bad sizes");
+    HYMT2_REQUIRE(taps >= 1 && taps <= CONV_MAX_TAPS, "causal_conv: %d taps; 1 to %d are taken", taps, CONV_MAX_TAPS);
+    HYMT2_REQUIRE(state_offset % 4 == 0 && state_stride % 4 == 0, "causal_conv: the state must be 4-byte aligned");
+    HYMT2_REQUIRE(ldx >= channels && ldo >= channels, "causal_conv: a row is shorter than the channels");
+    ConvParams p;
+    p.x = x; p.out = out; p.w = w; p.bias = bias; p.state = (uint8_t*)state + state_offset; p.state_stride = state_stride;
+    p.cu_seqlens = cu_seqlens; p.slot_ids = slot_ids; p.kv_lens = kv_lens;
+    p.channels = channels; p.taps = taps; p.ldx = ldx; p.ldo = ldo; p.add_input = add_input;
+    const int chunks = (max_new_tokens + CONV_CHUNK - 1) / CONV_CHUNK;
+    HYMT2_REQUIRE(chunks <= 65535, "causal_conv: %d tokens in one sequence are too many for one launch", max_new_tokens);
+    const dim3 grid((channels + CONV_THREADS - 1) / CONV_THREADS, chunks, batch);
+    HYMT2_DISPATCH_DTYPE(dtype, T, (causal_conv_kernel<T><<<grid, CONV_THREADS, 0, stream>>>(p)));
+    return hymt2_check_launch("causal_conv");
+}
+
+HYMT2_API int hymt2_rglru_scan(void* out, const float* gates, const void* u, const void* y, int dtype, const float* br,
+                               const float* bi, const float* lam, float decay, void* state, long state_offset,
+                               long state_stride, const int* cu_seqlens, const int* slot_ids, const int* kv_lens, int batch,
+                               int width, int ldu, int ldy, int ldo, cudaStream_t stream) {
+    if (batch == 0) return HYMT2_OK;
+    HYMT2_REQUIRE(batch > 0 && batch <= 65535 && width > 0, "rglru_scan: bad sizes");
+    HYMT2_REQUIRE(state_offset % 4 == 0 && state_stride % 4 == 0, "rglru_scan: the state must be 4-byte aligned");
+    ScanParams p;
+    p.gates = gates; p.u = u; p.y = y; p.out = out; p.br = br; p.bi = bi; p.lam = lam;
+    p.state = (uint8_t*)state + state_offset; p.state_stride = state_stride;
+    p.cu_seqlens = cu_seqlens; p.slot_ids = slot_ids; p.kv_lens = kv_lens;
+    p.width = width; p.ldu = ldu; p.ldy = ldy; p.ldo = ldo; p.decay = decay;
+    const dim3 grid((width + RG_THREADS - 1) / RG_THREADS, batch);
+    HYMT2_DISPATCH_DTYPE(dtype, T, (rglru_scan_kernel<T><<<grid, RG_THREADS, 0, stream>>>(p)));
+    return hymt2_check_launch("rglru_scan");
+}

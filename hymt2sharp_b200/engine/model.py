@@ -78,7 +78,7 @@ class DecoderModel:
                         planes[g] += 1
                 row.append(slot)
             self.slots.append(row)
-        self.groups = [GroupSpec(s.kind, s.kv_heads, s.head_dim, planes[g], s.window) for g, s in enumerate(specs)]
+        self.groups = [GroupSpec(s.kind, s.kv_heads, s.head_dim, planes[g], s.window, s.streams) for g, s in enumerate(specs)]
         self.state_bytes = offset
 
     # -- weights ------------------------------------------------------------------
@@ -146,4 +146,7 @@ class DecoderModel:
         # a model that scales its logits gives the factor to the final norm: (s * norm(x)) W = s * (norm(x) W)
         scale = {} if self.spec.logit_scale is None else {"scale": float(self.spec.logit_scale)}
         normed = self.final_norm.forward(residual, ctx, ctx.dtype, rows_index=want_rows, rows=num_want, **scale)
-        return self.head(normed, out_dtype=torch.float32)
+        logits = self.head(normed, out_dtype=torch.float32)
+        if self.spec.logit_softcap is not None:
+            ops.softcap(logits, float(self.spec.logit_softcap))
+        return logits

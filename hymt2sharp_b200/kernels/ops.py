@@ -795,3 +795,193 @@ def record_history(history: torch.Tensor, counts: torch.Tensor, tokens: torch.Te
     _need(tokens, "tokens", torch.int32, 1)
     _check(_lib().hymt2_record_history(_ptr(history), _ptr(counts), c_int(history.shape[1]), _ptr(tokens),
                                        _ptr(row_map), c_int(rows), _stream()), "record_history")
+
+
+# ---------------------------------------------------------------------------
+# grouped norm, short convolution, recurrence, small element-wise steps, shared-vector attention
+# ---------------------------------------------------------------------------
+def _f32(t: torch.Tensor | None, name: str, n: int | None = None) -> None:
+    if t is not None:
+        _need(t, name, torch.float32)
+        if n is not None and t.numel() != n:
+            raise KernelError(f"{name} must hold {n} values, got {t.numel()}")
+
+
+def rmsnorm_groups(out: torch.Tensor, x: torch.Tensor, gain: torch.Tensor, eps: float, groups: int,
+                   rows_index: torch.Tensor | None = None, out_scale: float = 1.0, add: bool = False) -> None:
+    """RMSNorm in `groups` equal consecutive parts of every row, each part with its own root mean square, the whole
+    times gain, in float32.  `add`: out (float32) += the result instead of out = the result."""
+    _need(out, "out", None, 2); _need(x, "x", None, 2); _need(gain, "gain", None, 1)
+    rows, dim = out.shape
+    if x.shape[1] != dim or gain.shape[0] != dim or groups <= 0 or dim % groups:
+        raise KernelError(f"rmsnorm_groups: shapes out {tuple(out.shape)} x {tuple(x.shape)} gain {tuple(gain.shape)} groups {groups}")
+    if rows_index is not None:
+        _need(rows_index, "rows_index", torch.int32, 1)
+        if rows_index.shape[0] < rows:
+            raise KernelError("rmsnorm_groups: rows_index is shorter than out")
+    elif x.shape[0] < rows:
+        raise KernelError("rmsnorm_groups: x has fewer rows than out")
+    if add and out.dtype != torch.float32:
+        raise KernelError("rmsnorm_groups: adding needs float32 rows")
+    _check(_lib().hymt2_rmsnorm_groups(_ptr(out), c_int(dtype_code(out.dtype)), _ptr(x), c_int(dtype_code(x.dtype)), _ptr(gain),
+                                       c_int(dtype_code(gain.dtype)), _ptr(rows_index), c_int(rows), c_int(dim), c_int(groups),
+                                       c_float(eps), c_float(out_scale), c_int(1 if add else 0), _stream()), "rmsnorm_groups")
+
+
+def _rows_view(t: torch.Tensor, name: str, dtype=None) -> int:
+    """A matrix whose rows are contiguous (it may be a view of some columns of a wider one); returns its row stride."""
+    if not t.is_cuda or t.dim() != 2 or t.stride(1) != 1:
+        raise KernelError(f"{name} must be a CUDA matrix with contiguous rows")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+    return t.stride(0)
+
+
+def causal_conv(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, state: torch.Tensor,
+                state_offset: int, cu_seqlens: torch.Tensor, slot_ids: torch.Tensor, kv_lens: torch.Tensor, batch: int,
+                max_new_tokens: int, add_input: bool) -> None:
+    """Causal convolution over time on each channel: out_t = (x_t if add_input) + bias + sum_j w[:, j] x_(t - taps + 1 + j),
+    zeros before a sequence's start.  `state` is the cache's byte matrix [slots, bytes]; from byte `state_offset` of a
+    slot's row lie float32 [taps - 1, channels], the sequence's last inputs, which the kernel reads and renews."""
+    ldx, ldo = _rows_view(x, "x"), _rows_view(out, "out", x.dtype)
+    T, C = x.shape
+    _f32(w, "w"); _f32(bias, "bias", C)
+    if out.shape != x.shape or w.dim() != 2 or w.shape[0] != C:
+        raise KernelError(f"causal_conv: shapes out {tuple(out.shape)} x {tuple(x.shape)} w {tuple(w.shape)}")
+    taps = w.shape[1]
+    if state.dtype != torch.uint8 or state.dim() != 2 or state_offset + 4 * (taps - 1) * C > state.shape[1]:
+        raise KernelError("causal_conv: the state rows are too short for this convolution")
+    for t, n in ((cu_seqlens, "cu_seqlens"), (slot_ids, "slot_ids"), (kv_lens, "kv_lens")):
+        _need(t, n, torch.int32, 1)
+    _check(_lib().hymt2_causal_conv(_ptr(out), _ptr(x), c_int(dtype_code(x.dtype)), _ptr(w), _ptr(bias), _ptr(state),
+                                    c_long(state_offset), c_long(state.stride(0)), _ptr(cu_seqlens), _ptr(slot_ids), _ptr(kv_lens),
+                                    c_int(batch), c_int(max_new_tokens), c_int(C), c_int(taps), c_int(ldx), c_int(ldo),
+                                    c_int(1 if add_input else 0), _stream()), "causal_conv")
+
+
+def rglru_scan(out: torch.Tensor, gates: torch.Tensor, u: torch.Tensor, y: torch.Tensor, br: torch.Tensor, bi: torch.Tensor,
+               lam: torch.Tensor, decay: float, state: torch.Tensor, state_offset: int, cu_seqlens: torch.Tensor,
+               slot_ids: torch.Tensor, kv_lens: torch.Tensor, batch: int) -> None:
+    """The real-gated linear recurrence over every sequence's new tokens, in float32: r = sigmoid(gates[:, :W] + br),
+    i = sigmoid(gates[:, W:] + bi), a = exp(-decay * r * softplus(lam)), S <- a S + sqrt(1 - a^2) i u, out = S * y.
+    S (float32 [W]) lies at byte `state_offset` of the sequence's state row."""
+    T, W = u.shape
+    ldu, ldy, ldo = _rows_view(u, "u"), _rows_view(y, "y", u.dtype), _rows_view(out, "out", u.dtype)
+    _need(gates, "gates", torch.float32, 2)
+    if gates.shape != (T, 2 * W) or y.shape != u.shape or out.shape != u.shape:
+        raise KernelError(f"rglru_scan: shapes gates {tuple(gates.shape)} u {tuple(u.shape)} y {tuple(y.shape)} out {tuple(out.shape)}")
+    _f32(br, "br", W); _f32(bi, "bi", W); _f32(lam, "lam", W)
+    if state.dtype != torch.uint8 or state.dim() != 2 or state_offset + 4 * W > state.shape[1]:
+        raise KernelError("rglru_scan: the state rows are too short")
+    for t, n in ((cu_seqlens, "cu_seqlens"), (slot_ids, "slot_ids"), (kv_lens, "kv_lens")):
+        _need(t, n, torch.int32, 1)
+    _check(_lib().hymt2_rglru_scan(_ptr(out), _ptr(gates), _ptr(u), _ptr(y), c_int(dtype_code(u.dtype)), _ptr(br), _ptr(bi), _ptr(lam),
+                                   c_float(decay), _ptr(state), c_long(state_offset), c_long(state.stride(0)), _ptr(cu_seqlens),
+                                   _ptr(slot_ids), _ptr(kv_lens), c_int(batch), c_int(W), c_int(ldu), c_int(ldy), c_int(ldo),
+                                   _stream()), "rglru_scan")
+
+
+def bias_act(x: torch.Tensor, bias: torch.Tensor | None, act_cols: int) -> None:
+    """In place: x += bias; the first `act_cols` columns then go through the tanh form of GELU."""
+    ld = _rows_view(x, "x")
+    _f32(bias, "bias", x.shape[1])
+    _check(_lib().hymt2_bias_act(_ptr(x), c_int(dtype_code(x.dtype)), _ptr(bias), c_int(x.shape[0]), c_int(x.shape[1]), c_long(ld),
+                                 c_int(act_cols), _stream()), "bias_act")
+
+
+def xielu(out: torch.Tensor, x: torch.Tensor, pq: torch.Tensor) -> None:
+    """out = xIELU(x) with pq = (p, q) float32 on the device: z > 0: softplus(p) z^2 + z/2; else (1/2 + softplus(q)) (e^z - 1 - z) + z/2."""
+    _need(out, "out", x.dtype); _need(x, "x"); _f32(pq, "pq", 2)
+    if out.shape != x.shape:
+        raise KernelError("xielu: shapes differ")
+    _check(_lib().hymt2_xielu(_ptr(out), _ptr(x), c_int(dtype_code(x.dtype)), _ptr(pq), c_long(x.numel()), _stream()), "xielu")
+
+
+def sigmoid_gate(x: torch.Tensor, g: torch.Tensor, heads: int, vdim: int, per_head: bool) -> None:
+    """In place on x [T, heads * vdim]: times sigmoid(g), where g has one column per head or one per entry."""
+    _need(x, "x", None, 2)
+    ldg = _rows_view(g, "g", x.dtype)
+    if x.shape[1] != heads * vdim or g.shape != (x.shape[0], heads if per_head else heads * vdim):
+        raise KernelError(f"sigmoid_gate: shapes x {tuple(x.shape)} g {tuple(g.shape)}")
+    _check(_lib().hymt2_sigmoid_gate(_ptr(x), _ptr(g), c_int(dtype_code(x.dtype)), c_int(x.shape[0]), c_int(heads), c_int(vdim),
+                                     c_long(ldg), c_int(1 if per_head else 0), _stream()), "sigmoid_gate")
+
+
+def softcap(logits: torch.Tensor, cap: float) -> None:
+    """In place: logits = cap * tanh(logits / cap)."""
+    _need(logits, "logits", torch.float32)
+    _check(_lib().hymt2_softcap(_ptr(logits), c_float(cap), c_long(logits.numel()), _stream()), "softcap")
+
+
+def gemm_simt_batched(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, batch: int, a_step: int, out_step: int,
+                      epilogue: int = EPILOGUE_STORE) -> None:
+    """`batch` products in one launch: product z is out[:, z*out_step : z*out_step + N] = a[:, z*a_step : z*a_step + K] @ w[z]^T
+    with w [batch, N, K]; a and out are matrices with contiguous rows (columns of wider buffers are fine)."""
+    lda, ldc = _rows_view(a, "a"), _rows_view(out, "out")
+    _need(w, "w", None, 3)
+    if w.shape[0] != batch or a.shape[0] != out.shape[0]:
+        raise KernelError(f"gemm_simt_batched: shapes out {tuple(out.shape)} a {tuple(a.shape)} w {tuple(w.shape)}")
+    N, K = w.shape[1], w.shape[2]
+    if (batch - 1) * a_step + K > a.shape[1] or (batch - 1) * out_step + N > out.shape[1]:
+        raise KernelError("gemm_simt_batched: the steps run past a row")
+    _check(_lib().hymt2_gemm_simt_batched(_ptr(out), c_int(dtype_code(out.dtype)), _ptr(a), c_int(dtype_code(a.dtype)), _ptr(w),
+                                          c_int(dtype_code(w.dtype)), c_int(out.shape[0]), c_int(N), c_int(K), c_long(lda), c_long(K),
+                                          c_long(ldc), c_int(batch), c_long(a_step), c_long(N * K), c_long(out_step), c_int(epilogue),
+                                          _stream()), "gemm_simt_batched")
+
+
+def latent_prep(proj: torch.Tensor, q_cols: int, q_out: torch.Tensor, cache_plane: torch.Tensor | None, block_table: torch.Tensor,
+                block_tokens: int, token_seq: torch.Tensor, token_pos: torch.Tensor, slot_ids: torch.Tensor, gain: torch.Tensor,
+                inv_freq: torch.Tensor | None, rot_dims: int, amplitude: float, eps: float, heads: int, dim: int, rot: int,
+                rank: int) -> None:
+    """From a token's fused projection [heads * (dim + rot) query entries | rank latent entries | rot shared key entries]:
+    the normed latent vector and the rotated shared key part go to the token's cache row [rank + rot]; every head's
+    rotated query part goes to q_out[t, h, rank : rank + rot].  Pairs (2i, 2i+1) turn by position * inv_freq[i], cosine
+    and sine times `amplitude`.  cache_plane None: nothing is cached."""
+    ldp = _rows_view(proj, "proj")
+    T = proj.shape[0]
+    dl = rank + rot
+    _need(q_out, "q_out", proj.dtype, 2)
+    if proj.shape[1] < q_cols + dl or q_cols != heads * (dim + rot) or q_out.shape != (T, heads * dl):
+        raise KernelError(f"latent_prep: shapes proj {tuple(proj.shape)} q_out {tuple(q_out.shape)}")
+    if cache_plane is not None:
+        _need(cache_plane, "cache_plane", proj.dtype, 4)
+        if cache_plane.shape[1:] != (1, block_tokens, dl):
+            raise KernelError(f"latent_prep: the cache plane is {tuple(cache_plane.shape)}, expected [blocks, 1, {block_tokens}, {dl}]")
+    _need(block_table, "block_table", torch.int32, 2)
+    for t, n in ((token_seq, "token_seq"), (token_pos, "token_pos"), (slot_ids, "slot_ids")):
+        _need(t, n, torch.int32, 1)
+    _f32(gain, "gain", rank); _f32(inv_freq, "inv_freq", rot_dims // 2)
+    _check(_lib().hymt2_latent_prep(_ptr(proj), c_long(ldp), c_int(q_cols), _ptr(q_out), _ptr(cache_plane), c_int(dtype_code(proj.dtype)),
+                                    _ptr(block_table), c_int(block_table.stride(0)), c_int(block_tokens), _ptr(token_seq),
+                                    _ptr(token_pos), _ptr(slot_ids), _ptr(gain), _ptr(inv_freq), c_int(rot_dims), c_float(amplitude),
+                                    c_float(eps), c_int(T), c_int(heads), c_int(dim), c_int(rot), c_int(rank), _stream()), "latent_prep")
+
+
+def attention_shared_vector(out: torch.Tensor, q: torch.Tensor, cache_plane: torch.Tensor, block_table: torch.Tensor,
+                            cu_seqlens: torch.Tensor, slot_ids: torch.Tensor, kv_lens: torch.Tensor, batch: int,
+                            max_new_tokens: int, nh: int, d: int, dv: int, scale: float, window: int = 0, split_keys: int = 0,
+                            max_splits: int = 0, part_acc: torch.Tensor | None = None, part_ml: torch.Tensor | None = None,
+                            status: torch.Tensor | None = None) -> None:
+    """Causal attention of the new tokens over a cache of ONE vector [d] per token that all heads share: it is every
+    head's key, and its first dv entries are every head's value.  q [T, nh * d], out [T, nh * dv]; CUDA cores, float32
+    scores and softmax.  Splits as attention_simt (the partials are [T, nh, splits, dv])."""
+    if status is None:
+        status = device_status(out.device)
+    _need(out, "out", None, 2); _need(q, "q", out.dtype, 2); _need(cache_plane, "cache_plane", out.dtype, 4)
+    T = out.shape[0]
+    if out.shape[1] != nh * dv or q.shape[1] != nh * d or q.shape[0] < T or cache_plane.shape[1] != 1 or cache_plane.shape[3] != d:
+        raise KernelError(f"attention_shared_vector: shapes out {tuple(out.shape)} q {tuple(q.shape)} cache {tuple(cache_plane.shape)}")
+    _need(block_table, "block_table", torch.int32, 2)
+    for t, n in ((cu_seqlens, "cu_seqlens"), (slot_ids, "slot_ids"), (kv_lens, "kv_lens")):
+        _need(t, n, torch.int32, 1)
+    if split_keys > 0:
+        _need(part_acc, "part_acc", torch.float32); _need(part_ml, "part_ml", torch.float32)
+        if part_acc.numel() < T * nh * max_splits * dv or part_ml.numel() < T * nh * max_splits * 2:
+            raise KernelError("attention_shared_vector: the split scratch is too small")
+    _check(_lib().hymt2_attention_shared_vector(_ptr(out), _ptr(q), _ptr(cache_plane), c_int(dtype_code(out.dtype)), _ptr(block_table),
+                                                c_int(block_table.stride(0)), c_int(cache_plane.shape[2]), _ptr(cu_seqlens),
+                                                _ptr(slot_ids), _ptr(kv_lens), c_int(batch), c_int(T), c_int(max_new_tokens),
+                                                c_int(nh), c_int(d), c_int(dv), c_float(scale), c_int(window), c_int(split_keys),
+                                                c_int(max_splits), _ptr(part_acc), _ptr(part_ml), _stream(), _ptr(status)),
+           "attention_shared_vector", 2 if split_keys > 0 else 1)

@@ -79,6 +79,8 @@ class GQAAttention:
         nh, nkv, d = self.heads, self.kv_heads, self.head_dim
         # the position encoding in the form that the appending kernels take, or None: it rotates q and k itself
         epilogue = self.position.kernel_epilogue(ctx) if self.position is not None else RotaryEpilogue.none()
+        if epilogue is not None and epilogue.rope_dim and epilogue.pairing != "half":
+            raise ValueError("the kernels of this attention rotate pairs (i, i + rope_dim/2); its position encoding offers another pairing")
         k_plane, v_plane = ctx.cache.plane(slot.group, slot.plane)
         block_table = ctx.cache.tables[slot.group]
         planes = (k_plane, v_plane) if slot.writes else (None, None)

@@ -27,8 +27,9 @@ Interfaces (duck-typed, see the classes in this package for examples):
   feed-forward
       forward(x [T, hidden], residual float32 [T, hidden], ctx) -> None
   block  (it may hold any number of mixers, none included; the model asks the block, never its parts)
-      cache_needs() -> [GroupSpec or None]   one entry per mixer it holds, in a fixed order
-      state_bytes() -> [int]                 one entry per mixer, same order
+      cache_needs() -> [GroupSpec or None]   one entry per mixer it holds, in a fixed order; a block may add entries
+                                             (None) for other parts of its own that remember something between steps
+      state_bytes() -> [int]                 one entry per entry of cache_needs(), same order
       graph_safe: bool                       every part it holds is graph_safe
       forward(residual, ctx, slots: [MixerSlot]) -> None     slots[i] belongs to the i-th mixer
 
@@ -73,7 +74,9 @@ class RotaryEpilogue:
     cache: dims i and i + rope_dim/2 are a pair, rotated by position * inv_freq[i]; dims from rope_dim on stay."""
     inv_freq: torch.Tensor | None     # float32 [rope_dim / 2] on the device; None with rope_dim 0
     rope_dim: int
-    pairing: str = "half"             # the only pairing the kernels know; anything else is refused by them
+    pairing: str = "half"             # "half": (i, i + rope_dim/2), what the key/value appending kernels know;
+                                      # "interleaved": (2i, 2i + 1), what the latent-attention kernels know
+    amplitude: float = 1.0            # cosine and sine are multiplied by this (1 unless the encoding scales them)
 
     @staticmethod
     def none() -> "RotaryEpilogue":

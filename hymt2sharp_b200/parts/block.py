@@ -61,3 +61,82 @@ class PreNormBlock:
 
 
 register_part("block", "pre_norm", PreNormBlock)
+
+
+class SandwichBlock:
+    """A block with a norm before AND after each sublayer, and an optional short convolution in front of each:
+
+        h = norm1(x);  h = h + conv1(h);  x += norm1b(mixer(h))
+        h = norm2(x);  h = h + conv2(h);  x += norm2b(ff(h))          (no feed-forward: the second line is absent)
+
+    The convolutions run over time on each channel (parts.conv.ShortConv); their last inputs are state of the
+    sequence, which this block asks the model for beside its mixer's: cache_needs() / state_bytes() have the mixer's
+    entry first, then one entry for each convolution it holds.  A sublayer's output is collected in a zeroed float32
+    buffer (mixers and feed-forwards add into what they are given) and joins the residual through the norm after it."""
+
+    def __init__(self, norm1: PartSpec, mixer: PartSpec, norm1_after: PartSpec, norm2: PartSpec | None = None,
+                 feed_forward: PartSpec | None = None, norm2_after: PartSpec | None = None, conv1: dict | None = None,
+                 conv2: dict | None = None):
+        from .conv import ShortConv
+        self.norm1 = build_part("norm", norm1)
+        self.mixer = build_part("mixer", mixer)
+        self.norm1_after = build_part("norm", norm1_after)
+        self.feed_forward = build_part("feed_forward", feed_forward) if feed_forward is not None else None
+        self.norm2 = build_part("norm", norm2) if feed_forward is not None else None
+        self.norm2_after = build_part("norm", norm2_after) if feed_forward is not None else None
+        self.conv1 = ShortConv(add_input=True, **conv1) if conv1 is not None else None
+        self.conv2 = ShortConv(add_input=True, **conv2) if conv2 is not None and feed_forward is not None else None
+
+    def parts(self):
+        return tuple(p for p in (self.norm1, self.conv1, self.mixer, self.norm1_after, self.norm2, self.conv2,
+                                 self.feed_forward, self.norm2_after) if p is not None)
+
+    def _convs(self):
+        return [c for c in (self.conv1, self.conv2) if c is not None]
+
+    def cache_needs(self) -> list:
+        return [self.mixer.cache_need()] + [None for _ in self._convs()]
+
+    def state_bytes(self) -> list:
+        return [int(self.mixer.state_bytes())] + [c.state_bytes() for c in self._convs()]
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(getattr(p, "graph_safe", False) for p in self.parts())
+
+    def tensors(self):
+        t = {}
+        for p in self.parts():
+            t.update(p.tensors())
+        return t
+
+    def load(self, weights, device, dtype):
+        for p in self.parts():
+            p.load(weights, device, dtype)
+
+    def first_norm(self):
+        return None   # what reads the residual first here is followed by a convolution, which wants the plain rows
+
+    def forward(self, residual, ctx, slots) -> None:
+        import torch
+        conv_slots = list(slots[1:])
+        ctx.weights_ahead = ctx.norm_ahead = None
+        h = self.norm1.forward(residual, ctx, ctx.dtype, fresh=True)
+        if self.conv1 is not None:
+            h = self.conv1.forward(h, ctx, conv_slots.pop(0))
+        branch = torch.zeros_like(residual)
+        self.mixer.forward(h, branch, ctx, slots[0])
+        ctx.prenormed = None
+        self.norm1_after.add_into(branch, residual)
+        if self.feed_forward is None:
+            return
+        h = self.norm2.forward(residual, ctx, ctx.dtype, fresh=True)
+        if self.conv2 is not None:
+            h = self.conv2.forward(h, ctx, conv_slots.pop(0))
+        branch.zero_()
+        self.feed_forward.forward(h, branch, ctx)
+        ctx.prenormed = None
+        self.norm2_after.add_into(branch, residual)
+
+
+register_part("block", "sandwich", SandwichBlock)

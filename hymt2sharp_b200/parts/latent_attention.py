@@ -1,0 +1,119 @@
+"""Latent (low-rank key/value) attention over the paged cache, as a mixer part.
+
+Per token the cache holds ONE row for all heads: the latent vector c (`kv_rank` entries, RMS-normed with a gain) and one
+rotated key part (`rot_dim` entries) that every head shares.  Head h's key is [W_uk[h] c, rotated part], its value
+W_uv[h] c.  Nothing per head is ever stored or rebuilt: the up-projections are moved to the other side of the products,
+
+    score_h(t, s) = ( (W_uk[h]^T q_h[:dim]) . c_s  +  rot(q_h[dim:]) . rot(k_s) ) * scale
+    out_h(t)      = W_uv[h] ( sum_s softmax_s(score_h(t, .)) c_s )
+
+so the attention runs in the compressed space, with a query of kv_rank + rot_dim entries per head against the cached
+row, whose first kv_rank entries are also the value.  Then an output gate (sigmoid of a projection of the mixer's
+input, one value per output entry or one per head) and the output projection.  Scores, softmax, the latent norm and
+the rotation are float32; the projections run in the engine's compute type.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..cache.allocator import GroupSpec
+from ..kernels import ops
+from ..weights.loader import TensorSpec
+from .base import MixerSlot, PartSpec, build_part, register_part
+from .linear import Linear, compute_form
+
+SPLIT_KEYS = 256  # decode: keys per partial, a constant so that the cut depends on nothing else
+
+
+class LatentAttention:
+    graph_safe = True  # its forward only launches kernels on the current stream
+
+    def __init__(self, hidden: int, heads: int, dim: int, rot_dim: int, vdim: int, kv_rank: int, scale: float, eps: float,
+                 position: PartSpec | None, gate: str | None, q_proj: str, dkv_proj: str, dkv_norm: str, uk_proj: str,
+                 uv_proj: str, o_proj: str, g_proj: str | None = None, window: int | None = None):
+        if gate not in (None, "element", "head"):
+            raise ValueError(f"output gate '{gate}': known are 'element' (one value per output entry), 'head' and None")
+        if gate is not None and g_proj is None:
+            raise ValueError("an output gate needs its projection's tensor name")
+        self.hidden, self.heads, self.dim, self.rot, self.vdim, self.rank = hidden, heads, dim, rot_dim, vdim, kv_rank
+        self.scale, self.eps, self.gate, self.window = float(scale), float(eps), gate, int(window or 0)
+        self.names = dict(q=q_proj, dkv=dkv_proj, cn=dkv_norm, uk=uk_proj, uv=uv_proj, o=o_proj, g=g_proj)
+        self.position = build_part("position", position) if position is not None else None
+        self.q_cols = heads * (dim + rot_dim)
+        self.gate_cols = 0 if gate is None else (heads * vdim if gate == "element" else heads)
+        self.proj = self.out = self.uk_t = self.uv = self.c_gain = None
+
+    # -- what it needs ----------------------------------------------------------
+    def tensors(self):
+        n, H = self.names, self.heads
+        t = {n["q"]: TensorSpec((self.q_cols, self.hidden)), n["dkv"]: TensorSpec((self.rank + self.rot, self.hidden)),
+             n["cn"]: TensorSpec((self.rank,), init="gain"), n["uk"]: TensorSpec((H * self.dim, self.rank)),
+             n["uv"]: TensorSpec((H * self.vdim, self.rank)), n["o"]: TensorSpec((self.hidden, H * self.vdim))}
+        if self.gate is not None:
+            t[n["g"]] = TensorSpec((self.gate_cols, self.hidden))
+        if self.position is not None:
+            t.update(self.position.tensors())
+        return t
+
+    def cache_need(self):
+        kind = "window" if self.window > 0 else "full"
+        return GroupSpec(kind, 1, self.rank + self.rot, planes=0, window=self.window, streams=1)
+
+    def state_bytes(self) -> int:
+        return 0
+
+    def load(self, weights, device, dtype):
+        n, H = self.names, self.heads
+        rows = [weights[n["q"]], weights[n["dkv"]]] + ([weights[n["g"]]] if self.gate is not None else [])
+        self.proj = Linear(compute_form(torch.cat(rows, dim=0), device, dtype), role="q_dkv_gate")
+        self.out = Linear(compute_form(weights[n["o"]], device, dtype), ops.EPILOGUE_ACCUMULATE, role="o_proj")
+        # per head: W_uk[h]^T [kv_rank, dim] (the query goes into the compressed space) and W_uv[h] [vdim, kv_rank]
+        uk = weights[n["uk"]].reshape(H, self.dim, self.rank).transpose(1, 2)
+        self.uk_t = compute_form(uk, device, dtype)
+        self.uv = compute_form(weights[n["uv"]].reshape(H, self.vdim, self.rank), device, dtype)
+        self.c_gain = weights[n["cn"]].to(device).float().contiguous()
+        if self.position is not None:
+            self.position.load(weights, device, dtype)
+
+    # -- the step ---------------------------------------------------------------
+    def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx, slot: MixerSlot) -> None:
+        T, H, dl = ctx.num_tokens, self.heads, self.rank + self.rot
+        rotary = self.position.kernel_epilogue(ctx) if self.position is not None else None
+        if rotary is not None and rotary.rope_dim and rotary.pairing != "interleaved":
+            raise ValueError("latent attention rotates neighbouring pairs; its position encoding must offer that form")
+        plane, _ = ctx.cache.plane(slot.group, slot.plane)
+        table = ctx.cache.tables[slot.group]
+        proj = self.proj(x, ctx=ctx)                                   # [T, queries | latent row | gate]
+        q = torch.empty((T, H * dl), dtype=proj.dtype, device=proj.device)
+        ops.latent_prep(proj, self.q_cols, q, plane if slot.writes else None, table, ctx.cache.block_tokens, ctx.token_seq,
+                        ctx.token_pos, ctx.slot_ids, self.c_gain, rotary.inv_freq if rotary else None,
+                        rotary.rope_dim if rotary else 0, rotary.amplitude if rotary else 1.0, self.eps, H, self.dim,
+                        self.rot, self.rank)
+        # q[t, h, :kv_rank] = W_uk[h]^T q_h[:dim]
+        ops.tag = "q_absorb"
+        ops.gemm_simt_batched(q, proj, self.uk_t, H, self.dim + self.rot, dl)
+        ops.tag = None
+        mixed = torch.empty((T, H * self.rank), dtype=q.dtype, device=q.device)
+        self.attend(mixed, q, plane, table, ctx)
+        out = torch.empty((T, H * self.vdim), dtype=q.dtype, device=q.device)
+        ops.tag = "v_up"
+        ops.gemm_simt_batched(out, mixed, self.uv, H, self.rank, self.vdim)
+        ops.tag = None
+        if self.gate is not None:
+            g0 = self.q_cols + dl
+            ops.sigmoid_gate(out, proj[:, g0:g0 + self.gate_cols], H, self.vdim, self.gate == "head")
+        self.out.add_then_norm(out, residual, getattr(ctx, "norm_ahead", None), ctx)
+
+    def attend(self, out, q, plane, table, ctx) -> None:
+        split, max_splits, acc, ml = 0, 0, None, None
+        if ctx.decode and ctx.max_kv_len > SPLIT_KEYS:
+            split = SPLIT_KEYS
+            max_splits = -(-ctx.max_kv_len // SPLIT_KEYS)
+            acc = torch.empty(ctx.num_tokens * self.heads * max_splits * self.rank, dtype=torch.float32, device=out.device)
+            ml = torch.empty(ctx.num_tokens * self.heads * max_splits * 2, dtype=torch.float32, device=out.device)
+        ops.attention_shared_vector(out, q, plane, table, ctx.cu_seqlens, ctx.slot_ids, ctx.kv_lens, ctx.num_seqs,
+                                    ctx.max_new_tokens, self.heads, self.rank + self.rot, self.rank, self.scale, self.window,
+                                    split, max_splits, acc, ml)
+
+
+register_part("mixer", "latent_attention", LatentAttention)

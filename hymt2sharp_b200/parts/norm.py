@@ -1,5 +1,7 @@
 """RMSNorm part: y = x / sqrt(mean(x^2) + eps) * gain
-(src/HyMT2Sharp/Ops.cs:29-89)."""
+(src/HyMT2Sharp/Ops.cs:29-89).  With `groups` > 1 a row is cut into that many equal
+consecutive parts and each part is divided by its own root mean square; the gain
+spans the whole row."""
 from __future__ import annotations
 
 import torch
@@ -12,10 +14,14 @@ from .linear import compute_form
 
 class RMSNorm:
     graph_safe = True  # its forward only launches kernels on the current stream
-    foldable = True    # y = x * r * gain with a row scale r: the products around it can take it over (parts.base.Prenormed)
 
-    def __init__(self, dim: int, eps: float, weight: str):
-        self.dim, self.eps, self.weight_name = int(dim), float(eps), weight
+    def __init__(self, dim: int, eps: float, weight: str, groups: int = 1):
+        self.dim, self.eps, self.weight_name, self.groups = int(dim), float(eps), weight, int(groups)
+        if self.groups < 1 or self.dim % self.groups:
+            raise ValueError(f"a norm over {dim} entries cannot be cut into {groups} equal parts")
+        # y = x * r * gain with ONE row scale r: the products around it can take it over (parts.base.Prenormed);
+        # with several parts a row has several scales, and the norm runs as its own kernel
+        self.foldable = self.groups == 1
         self.gain = None
 
     def tensors(self):
@@ -35,8 +41,15 @@ class RMSNorm:
                 return pre
         n = rows if rows is not None else (rows_index.shape[0] if rows_index is not None else x.shape[0])
         out = torch.empty((n, self.dim), dtype=out_dtype, device=x.device)
-        ops.rmsnorm(out, x, self.gain, self.eps, rows_index, scale)
+        if self.groups == 1:
+            ops.rmsnorm(out, x, self.gain, self.eps, rows_index, scale)
+        else:
+            ops.rmsnorm_groups(out, x, self.gain, self.eps, self.groups, rows_index, scale)
         return out
+
+    def add_into(self, x: torch.Tensor, residual: torch.Tensor) -> None:
+        """residual (float32) += norm(x): a sublayer's output that is normed before it joins the residual stream."""
+        ops.rmsnorm_groups(residual, x, self.gain, self.eps, self.groups, add=True)
 
 
 register_part("norm", "rmsnorm", RMSNorm)

@@ -55,3 +55,57 @@ class NeoXRotary:
 
 
 register_part("position", "neox_rope", NeoXRotary)
+
+
+class YarnInterleavedRotary:
+    """Rotary encoding on neighbouring pairs with YaRN frequency scaling.
+
+    Of a vector's first `dims` entries, (2i, 2i+1) are a pair that turns by position * f_i, with
+    f_i = base^(-2i/dims).  With `scaling` = (factor, original, fast, slow): a pair index is mapped to
+    where a wavelength of `original / turns` positions falls, dim(turns) = dims * ln(original / (2 pi turns)) /
+    (2 ln base); lo = max(floor(dim(fast)), 0), hi = min(ceil(dim(slow)), dims - 1), ramp_i = clamp((i - lo) /
+    max(hi - lo, 0.001), 0, 1); the frequency becomes f_i / factor * ramp_i + f_i * (1 - ramp_i), and cosine and sine
+    are multiplied by 0.1 * ln(factor) + 1 (the `amplitude` of the epilogue).
+    The table is computed on the host in float64 and rounded to float32 once; the angle is the float32 product
+    position * f_i in the kernels.
+    """
+
+    def __init__(self, dims: int, base: float, scaling: dict | None = None):
+        if dims % 2 or dims < 0:
+            raise ValueError(f"{dims} rotated entries: the number must be even")
+        self.dims, self.base, self.scaling = int(dims), float(base), dict(scaling) if scaling else None
+        half = self.dims // 2
+        f = np.array([self.base ** (-2.0 * i / self.dims) for i in range(half)], dtype=np.float64)
+        self.amplitude = 1.0
+        if self.scaling:
+            factor, original = float(self.scaling["factor"]), float(self.scaling["original"])
+            fast, slow = float(self.scaling["fast"]), float(self.scaling["slow"])
+
+            def dim_of(turns: float) -> float:
+                return self.dims * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(self.base))
+
+            lo = max(math.floor(dim_of(fast)), 0)
+            hi = min(math.ceil(dim_of(slow)), self.dims - 1)
+            ramp = np.clip((np.arange(half, dtype=np.float64) - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+            f = f / factor * ramp + f * (1.0 - ramp)
+            self.amplitude = 0.1 * math.log(factor) + 1.0
+        self._host = f.astype(np.float32)
+        self.inv_freq = None
+
+    def tensors(self):
+        return {}
+
+    def load(self, weights, device, dtype):
+        key = (str(torch.device(device)), self._host.tobytes())
+        if key not in _TABLES:
+            _TABLES[key] = torch.from_numpy(self._host).to(device)
+        self.inv_freq = _TABLES[key]
+
+    def kernel_epilogue(self, ctx) -> RotaryEpilogue:
+        return RotaryEpilogue(self.inv_freq if self.dims else None, self.dims, pairing="interleaved", amplitude=self.amplitude)
+
+    def apply(self, qkv, ctx, heads, kv_heads, head_dim):
+        raise NotImplementedError("YarnInterleavedRotary is applied by the kernels that take an interleaved epilogue")
+
+
+register_part("position", "yarn_interleaved", YarnInterleavedRotary)
