@@ -142,6 +142,10 @@ class Engine:
         there (src/HyMT2Sharp/HunyuanDenseModel.cs:187-240, TruncateCache).  Whole blocks behind the new end go
         back to the pool.  A layer group with a window may already have handed back blocks that the shorter
         sequence would need again: that is refused (CacheError), nothing changes."""
+        if self.model.state_bytes and 0 < int(length) < self.cache.length(slot):
+            # a recurrent state or a convolution's last inputs are those of the sequence's END: they cannot be wound back
+            raise EngineError(f"slot {slot}: a model with per-sequence state can only be reset to an empty sequence, "
+                              f"not cut to {length} tokens")
         with torch.cuda.device(self.device):
             self.cache.truncate(slot, int(length))
 
