@@ -234,8 +234,11 @@ class DecodeSession:
     def _capture_graph(self, timed: bool):
         # one eager step first (it also sets up what kernels set up at their first launch), then
         # the capture, which runs nothing: the state that the eager step changed is put back
+        # (keys and values are written to the same rows again by the step that follows; a recurrent state or a
+        # convolution's last inputs would be moved on twice, so the sequences' state rows are put back as well)
         b = self.buf
         saved = b.meta.clone()
+        state = self.cache.state.clone() if self.cache.state_bytes else None
         rng = self.sampler.snapshot()
         stream = torch.cuda.Stream(device=self.engine.device)
         stream.wait_stream(torch.cuda.current_stream())
@@ -243,6 +246,8 @@ class DecodeSession:
             self._launch()
         torch.cuda.current_stream().wait_stream(stream)
         b.meta.copy_(saved)
+        if state is not None:
+            self.cache.state.copy_(state)
         self.sampler.restore(rng)
         before = ops.launches
         graph, events = torch.cuda.CUDAGraph(), []

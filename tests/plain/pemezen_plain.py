@@ -84,9 +84,11 @@ def rotate_pairs(v: torch.Tensor, positions: torch.Tensor, f: torch.Tensor, m: f
 
 
 # -- latent attention ---------------------------------------------------------------------------------
-def latent_attention(h: torch.Tensor, W: dict, mixer: dict, gate: str, eps: float) -> torch.Tensor:
+def latent_attention(h: torch.Tensor, W: dict, mixer: dict, gate: str | None, eps: float, window: int = 0,
+                     return_weights: bool = False) -> torch.Tensor:
     """h [T, width] of ONE sequence from position 0.  W: this mixer's tensors by their short names.
-    gate: "element" (sigmoid(W_g h) has one entry per output channel) or "head" (one per head)."""
+    gate: "element" (sigmoid(W_g h) has one entry per output channel), "head" (one per head) or None.
+    window > 0: position t sees only the keys s with t - window < s <= t (the design itself has none)."""
     T = h.shape[0]
     H, dim, rot, vdim, rank = mixer["heads"], mixer["dim"], mixer["rot_dim"], mixer["vdim"], mixer["kv_rank"]
     pos = torch.arange(T)
@@ -102,11 +104,16 @@ def latent_attention(h: torch.Tensor, W: dict, mixer: dict, gate: str, eps: floa
     v = (c @ W["uv"].T).reshape(T, H, vdim)
     scores = (torch.einsum("thd,shd->hts", q[..., :dim], k) + torch.einsum("thd,sd->hts", q_rot, k_rot)) * mixer["scale"]
     visible = pos[None, :] <= pos[:, None]
+    if window > 0:
+        visible = visible & (pos[None, :] > pos[:, None] - window)
     scores = scores.masked_fill(~visible[None], float("-inf"))
     p = torch.softmax(scores, dim=-1)
+    if return_weights:
+        return p
     out = torch.einsum("hts,shd->thd", p, v)
-    g = torch.sigmoid(h @ W["g"].T)
-    out = out * (g.reshape(T, H, vdim) if gate == "element" else g.reshape(T, H, 1))
+    if gate is not None:
+        g = torch.sigmoid(h @ W["g"].T)
+        out = out * (g.reshape(T, H, vdim) if gate == "element" else g.reshape(T, H, 1))
     return out.reshape(T, H * vdim) @ W["o"].T
 
 
