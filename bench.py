@@ -140,6 +140,131 @@ def reference_arm() -> int:
     return 0
 
 
+# ---- another design beside the flagship: `--design pemezen` -----------------------------------------------------------------
+# Sizes that resemble a real model's layers (random weights), and a Hunyuan-dense model of the same width, depth and
+# nearly the same number of weights per layer beside it: the closest model that the library has.
+DESIGN_SIZES = {
+    "s": dict(width=1024, vocab=32768, ff=4096, heads=8, dim=64, rot_dim=32, vdim=64, kv_rank=256, rec_width=1024, rec_blocks=8,
+              dense=dict(num_attention_heads=8, num_key_value_heads=2, intermediate_size=2816)),
+    "m": dict(width=2048, vocab=65536, ff=8192, heads=16, dim=128, rot_dim=64, vdim=128, kv_rank=512, rec_width=2560, rec_blocks=10,
+              dense=dict(num_attention_heads=16, num_key_value_heads=4, intermediate_size=5632)),
+}
+DESIGN_ORDER = ["latent_attention_2", "latent_attention", "rglru", "latent_attention_2"]   # repeated up to --layers
+
+
+def make_design_models(size: str, layers: int) -> dict:
+    """Model folders with random weights: {"pemezen": ..., "hunyuan_dense": ...}."""
+    from hymt2sharp_b200.config import HunyuanDenseConfig, PemezenConfig
+    from hymt2sharp_b200.weights import write_random_model
+    z = DESIGN_SIZES[size]
+    rot = dict(dims=z["rot_dim"], base=10000.0, scaling=dict(factor=8.0, original=1024, fast=32.0, slow=1.0))
+    entries = []
+    for i in range(layers):
+        kind = DESIGN_ORDER[i % len(DESIGN_ORDER)]
+        if kind == "rglru":
+            mixer = dict(width=z["rec_width"], blocks=z["rec_blocks"], conv=4)
+        else:
+            mixer = dict(heads=z["heads"], dim=z["dim"], rot_dim=z["rot_dim"], vdim=z["vdim"], kv_rank=z["kv_rank"],
+                         scale=(z["dim"] + z["rot_dim"]) ** -0.5, rot=rot)
+        entries.append(dict(type=kind, mixer=mixer, mlp=dict(kind="dense", ff=z["ff"])))
+    new = PemezenConfig.from_dict(dict(architecture="Pemezen", vocab=z["vocab"], width=z["width"], layers=entries,
+                                       norm=dict(eps=1e-6, groups=2), canon=dict(taps=4), embedding=dict(scale=1.0), logit_softcap=30.0))
+    old = HunyuanDenseConfig.from_dict(dict(COMMON, architectures=["HunYuanDenseV1ForCausalLM"], num_hidden_layers=layers,
+                                            hidden_size=z["width"], vocab_size=z["vocab"], tie_word_embeddings=False,
+                                            rope_scaling={"type": "dynamic", "alpha": 1000.0}, **z["dense"]))
+    old_data = {k: v for k, v in old.to_dict().items()}
+    folders = {}
+    for name, cfg in (("pemezen", new), ("hunyuan_dense", HunyuanDenseConfig.from_dict(old_data))):
+        folders[name] = write_random_model(tempfile.mkdtemp(prefix=f"hymt2_bench_{name}_"), cfg, 7, 0.02)
+    return folders
+
+
+def design_bench(args) -> int:
+    """Prefill and decode throughput of the Pemezen design beside the Hunyuan-dense model of equal size, with each phase's
+    kernels timed one by one (CUDA events between launches; a captured decode step is stamped by the device's clock)."""
+    import numpy as np
+    import torch
+    import hymt2sharp_b200
+    from hymt2sharp_b200.engine.decode_session import DecodeSession
+    from hymt2sharp_b200.engine.engine import StepEntry
+    from hymt2sharp_b200.kernels import ops
+    from hymt2sharp_b200.sampling import BatchSampler, GREEDY
+
+    pk, pk_source = peaks()
+    z = DESIGN_SIZES[args.design_size]
+    layers = args.layers or 8
+    batch, context, steps, warmup = args.batch or 8, args.prefill, max(1, args.decode or args.steps or 32), max(3, args.warmup)
+    dtype = {"bf16": "bfloat16", "fp32": "float32"}[args.dtype]
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    rng = np.random.default_rng(99)
+    folders = make_design_models(args.design_size, layers)
+    out = {"design": "pemezen", "size": args.design_size, "layers": layers, "dtype": args.dtype, "data": "synthetic (random weights, random token ids)",
+           "sizes": {k: v for k, v in z.items() if k != "dense"}, "closest": dict(z["dense"], hidden_size=z["width"], head_dim=COMMON["head_dim"]),
+           "prefill_tokens": context, "decode": {"batch": batch, "context": context, "steps": steps}, "peaks": pk_source, "models": {}}
+    launches0 = ops.launches
+    try:
+        for name, folder in folders.items():
+            capacity = batch * (-(-(context + warmup + steps + 8) // 64) * 64) + context + 4096
+            engine = hymt2sharp_b200.load(folder, dtype=dtype, max_tokens=capacity, max_batch=batch)
+            res = {"weight_bytes_per_step": engine.model.streamed_weight_bytes(), "cache_bytes_per_token": engine.cache.bytes_per_token()}
+            prompt = rng.integers(0, z["vocab"], context).tolist()
+            times = []
+            for rep in range(2 + args.reps):
+                slot = engine.alloc_slots(1)
+                t0, t1 = ev(), ev()
+                torch.cuda.synchronize()
+                t0.record()
+                engine.step([StepEntry(slot[0], prompt, [context - 1])])
+                t1.record()
+                torch.cuda.synchronize()
+                engine.free_slots(slot)
+                if rep >= 2:
+                    times.append(t0.elapsed_time(t1))
+            res["prefill_ms"] = sum(times) / len(times)
+            res["prefill_tok_s"] = context / res["prefill_ms"] * 1000.0
+            slot = engine.alloc_slots(1)
+            ops.profile_begin()
+            engine.step([StepEntry(slot[0], prompt, [context - 1])])
+            res["prefill_kernels_ms"] = {k: round(v, 4) for k, v in ops.profile_end().items()}
+            engine.free_slots(slot)
+            # decode: `batch` sequences of `context` tokens, one token each a step, the step replayed from its CUDA graph
+            slots = engine.alloc_slots(batch)
+            firsts = [engine.step([StepEntry(s, rng.integers(0, z["vocab"], context).tolist(), [context - 1])]) for s in slots]
+            sampler = BatchSampler([GREEDY] * batch, engine.device)
+            first = sampler.sample(torch.cat(firsts), None)
+            session = DecodeSession(engine, slots, sampler, first, context + 2 * warmup + 2 * steps + 8, use_graph=not args.no_graph)
+            for _ in range(warmup):
+                session.step()
+            t0, t1 = ev(), ev()
+            torch.cuda.synchronize()
+            t0.record()
+            for _ in range(steps):
+                session.step()
+            t1.record()
+            torch.cuda.synchronize()
+            ms = t0.elapsed_time(t1) / steps
+            res["decode_ms_per_step"] = ms
+            res["decode_tok_s"] = batch / ms * 1000.0
+            step_bytes = res["weight_bytes_per_step"] + batch * (context + warmup + steps / 2) * res["cache_bytes_per_token"]
+            res["decode_hbm_frac"] = step_bytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"]
+            res["kernels_per_decode_step"] = session.kernels_per_step
+            ops.profile_begin()
+            for _ in range(4):
+                session.step()
+            res["decode_kernels_ms"] = {k: round(v / 4, 5) for k, v in ops.profile_end().items()}
+            engine.check()
+            engine.free_slots(slots)
+            out["models"][name] = res
+            del engine, session
+            torch.cuda.empty_cache()
+    finally:
+        for folder in folders.values():
+            shutil.rmtree(folder, ignore_errors=True)
+    out["gpu_launches"] = ops.launches - launches0
+    print(json.dumps(out))
+    return 0
+
+
 def make_model(config: str, layers: int) -> str:
     """A model folder with random weights of the named sizes (N(0, 0.02), the configuration's seed), in a temporary folder."""
     from hymt2sharp_b200.config import HunyuanDenseConfig
@@ -267,9 +392,15 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--no-kernels", action="store_true", help="skip the kernels timed alone")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--design", default=None, choices=["pemezen"],
+                    help="instead of the flagship workload: prefill (--prefill tokens) and decode (--batch sequences of --prefill tokens, "
+                         "--steps steps) of this design beside the Hunyuan-dense model of equal size, with per-kernel times")
+    ap.add_argument("--design-size", default="s", choices=sorted(DESIGN_SIZES))
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
+    if args.design is not None and args.gpus == 1:
+        return design_bench(args)
     if args.gpus != 1:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
         return 2

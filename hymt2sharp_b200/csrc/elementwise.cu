@@ -13,6 +13,8 @@ __device__ __forceinline__ float gelu_tanh_f(float z) {
 // x[r, c] <- act(x[r, c] + bias[c]); the first `act_cols` columns get the tanh form of GELU, the others the bias alone.
 template <typename T>
 __global__ void bias_act_kernel(T* __restrict__ x, const float* __restrict__ bias, int cols, long ld, int act_cols, size_t total) {
+    pdl_wait();   // everything in front is complete before anything is read; then the next kernel may be set up meanwhile
+    pdl_launch_dependents();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     const size_t r = i / cols;
@@ -27,6 +29,8 @@ __global__ void bias_act_kernel(T* __restrict__ x, const float* __restrict__ bia
 // for z <= 0  (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2.
 template <typename T>
 __global__ void xielu_kernel(T* __restrict__ out, const T* __restrict__ x, const float* __restrict__ pq, size_t total) {
+    pdl_wait();   // everything in front is complete before anything is read; then the next kernel may be set up meanwhile
+    pdl_launch_dependents();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     const float ap = softplus_e(pq[0]), an = 0.5f + softplus_e(pq[1]);
@@ -39,6 +43,8 @@ __global__ void xielu_kernel(T* __restrict__ out, const T* __restrict__ x, const
 template <typename T>
 __global__ void sigmoid_gate_kernel(T* __restrict__ x, const T* __restrict__ g, int heads, int vdim, long ldg, int per_head,
                                     size_t total) {
+    pdl_wait();   // everything in front is complete before anything is read; then the next kernel may be set up meanwhile
+    pdl_launch_dependents();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     const int width = heads * vdim;
@@ -50,6 +56,8 @@ __global__ void sigmoid_gate_kernel(T* __restrict__ x, const T* __restrict__ g, 
 
 // x <- cap * tanh(x / cap)
 __global__ void softcap_kernel(float* __restrict__ x, float cap, size_t total) {
+    pdl_wait();   // everything in front is complete before anything is read; then the next kernel may be set up meanwhile
+    pdl_launch_dependents();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     x[i] = cap * tanhf(x[i] / cap);
@@ -63,14 +71,14 @@ HYMT2_API int hymt2_bias_act(void* x, int dtype, const float* bias, int rows, in
     if (rows == 0 || cols == 0) return HYMT2_OK;
     HYMT2_REQUIRE(rows > 0 && cols > 0 && ld >= cols && act_cols >= 0 && act_cols <= cols, "bias_act: bad sizes");
     const size_t total = (size_t)rows * cols;
-    HYMT2_DISPATCH_DTYPE(dtype, T, (bias_act_kernel<T><<<blocks_for(total), 256, 0, stream>>>((T*)x, bias, cols, ld, act_cols, total)));
+    HYMT2_DISPATCH_DTYPE(dtype, T, launch_pdl(bias_act_kernel<T>, dim3(blocks_for(total)), dim3(256), 0, stream, (T*)x, bias, cols, ld, act_cols, total));
     return hymt2_check_launch("bias_act");
 }
 
 HYMT2_API int hymt2_xielu(void* out, const void* x, int dtype, const float* pq, long total, cudaStream_t stream) {
     if (total == 0) return HYMT2_OK;
     HYMT2_REQUIRE(total > 0 && pq != nullptr, "xielu: bad sizes");
-    HYMT2_DISPATCH_DTYPE(dtype, T, (xielu_kernel<T><<<blocks_for((size_t)total), 256, 0, stream>>>((T*)out, (const T*)x, pq, (size_t)total)));
+    HYMT2_DISPATCH_DTYPE(dtype, T, launch_pdl(xielu_kernel<T>, dim3(blocks_for((size_t)total)), dim3(256), 0, stream, (T*)out, (const T*)x, pq, (size_t)total));
     return hymt2_check_launch("xielu");
 }
 
@@ -79,14 +87,13 @@ HYMT2_API int hymt2_sigmoid_gate(void* x, const void* g, int dtype, int rows, in
     if (rows == 0) return HYMT2_OK;
     HYMT2_REQUIRE(rows > 0 && heads > 0 && vdim > 0, "sigmoid_gate: bad sizes");
     const size_t total = (size_t)rows * heads * vdim;
-    HYMT2_DISPATCH_DTYPE(dtype, T, (sigmoid_gate_kernel<T><<<blocks_for(total), 256, 0, stream>>>((T*)x, (const T*)g, heads, vdim, ldg,
-                                                                                               per_head, total)));
+    HYMT2_DISPATCH_DTYPE(dtype, T, launch_pdl(sigmoid_gate_kernel<T>, dim3(blocks_for(total)), dim3(256), 0, stream, (T*)x, (const T*)g, heads, vdim, ldg, per_head, total));
     return hymt2_check_launch("sigmoid_gate");
 }
 
 HYMT2_API int hymt2_softcap(float* x, float cap, long total, cudaStream_t stream) {
     if (total == 0) return HYMT2_OK;
     HYMT2_REQUIRE(total > 0 && cap > 0.f, "softcap: bad arguments");
-    softcap_kernel<<<blocks_for((size_t)total), 256, 0, stream>>>(x, cap, (size_t)total);
+    launch_pdl(softcap_kernel, dim3(blocks_for((size_t)total)), dim3(256), 0, stream, x, cap, (size_t)total);
     return hymt2_check_launch("softcap");
 }

@@ -134,6 +134,62 @@ int launch(void* C, const void* A, const void* W, int M, int N, int K, long lda,
     return hymt2_check_launch("gemm_simt");
 }
 
+
+// Few rows (a decode step's tokens) against a batch of small matrices: one warp per output column reads its weight
+// row once, 16 bytes a lane, and keeps a float32 sum for every row of A; the sums of a row do not depend on how many
+// other rows there are.  The time is that of reading W once.
+constexpr int SKINNY_MAX_ROWS = 16, SKINNY_WARPS = 8;
+
+template <typename T, typename TC>
+__global__ void __launch_bounds__(SKINNY_WARPS * 32)
+gemm_skinny_batched_kernel(TC* __restrict__ C, const T* __restrict__ A, const T* __restrict__ W, int M, int N, int K,
+                           long lda, long ldc, long a_bs, long w_bs, long c_bs, bool vec) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n = blockIdx.x * SKINNY_WARPS + warp;
+    if (n >= N) return;
+    A += (size_t)blockIdx.y * a_bs;
+    C += (size_t)blockIdx.y * c_bs;
+    const T* w = W + (size_t)blockIdx.y * w_bs + (size_t)n * K;
+    float acc[SKINNY_MAX_ROWS];
+#pragma unroll
+    for (int m = 0; m < SKINNY_MAX_ROWS; m++) acc[m] = 0.f;
+    constexpr int V = 16 / sizeof(T);
+    if (vec) {
+        for (int k = lane * V; k < K; k += 32 * V) {
+            float wv[V];
+            const uint4 raw = *reinterpret_cast<const uint4*>(w + k);
+            const T* wt = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+            for (int i = 0; i < V; i++) wv[i] = to_float(wt[i]);
+#pragma unroll
+            for (int m = 0; m < SKINNY_MAX_ROWS; m++) {
+                if (m < M) {
+                    const uint4 ra = *reinterpret_cast<const uint4*>(A + (size_t)m * lda + k);
+                    const T* at = reinterpret_cast<const T*>(&ra);
+#pragma unroll
+                    for (int i = 0; i < V; i++) acc[m] = fmaf(to_float(at[i]), wv[i], acc[m]);
+                }
+            }
+        }
+    } else {
+        for (int k = lane; k < K; k += 32) {
+            const float wv = to_float(w[k]);
+#pragma unroll
+            for (int m = 0; m < SKINNY_MAX_ROWS; m++)
+                if (m < M) acc[m] = fmaf(to_float(A[(size_t)m * lda + k]), wv, acc[m]);
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < SKINNY_MAX_ROWS; m++) {
+        if (m < M) {
+            const float v = warp_sum(acc[m]);
+            if (lane == 0) C[(size_t)m * ldc + n] = from_float<TC>(v);
+        }
+    }
+}
+
 }  // namespace
 
 // C[M,N] (ldc) = epilogue(A[M,K] (lda) · W[N,K]^T (ldw)); for the swiglu epilogue W has 2N rows.
@@ -164,4 +220,20 @@ HYMT2_API int hymt2_gemm_simt_batched(void* C, int c_dtype, const void* A, int a
     HYMT2_DISPATCH_DTYPE(a_dtype, TA, HYMT2_DISPATCH_DTYPE(w_dtype, TW, HYMT2_DISPATCH_DTYPE(c_dtype, TC,
         return (launch<TA, TW, TC>(C, A, W, M, N, K, lda, ldw, ldc, epilogue, stream, batch, a_bs, w_bs, c_bs)))));
     return HYMT2_OK;
+}
+
+// The same batch for at most 16 rows of A, A and W of one type (see gemm_skinny_batched_kernel): store epilogue only.
+HYMT2_API int hymt2_gemm_skinny_batched(void* C, int c_dtype, const void* A, const void* W, int dtype, int M, int N, int K,
+                                        long lda, long ldc, int batch, long a_bs, long w_bs, long c_bs, cudaStream_t stream) {
+    if (M == 0 || N == 0 || batch == 0) return HYMT2_OK;
+    HYMT2_REQUIRE(M > 0 && M <= SKINNY_MAX_ROWS && N > 0 && K > 0 && batch > 0 && batch <= 65535, "gemm_skinny: bad sizes M=%d N=%d K=%d batch=%d", M, N, K, batch);
+    HYMT2_REQUIRE(lda >= K && ldc >= N, "gemm_skinny: a leading dimension is smaller than its row");
+    const dim3 grid((N + SKINNY_WARPS - 1) / SKINNY_WARPS, batch);
+    HYMT2_DISPATCH_DTYPE(dtype, T, {
+        const long v = 16 / sizeof(T);
+        const bool vec = K % v == 0 && lda % v == 0 && a_bs % v == 0 && w_bs % v == 0 && (uintptr_t)A % 16 == 0 && (uintptr_t)W % 16 == 0;
+        HYMT2_DISPATCH_DTYPE(c_dtype, TC, launch_pdl(gemm_skinny_batched_kernel<T, TC>, grid, dim3(SKINNY_WARPS * 32), 0, stream, (TC*)C,
+                                                     (const T*)A, (const T*)W, M, N, K, lda, ldc, a_bs, w_bs, c_bs, vec));
+    });
+    return hymt2_check_launch("gemm_skinny_batched");
 }

@@ -39,6 +39,8 @@ latent_prep_kernel(LatentPrepParams p) {
     extern __shared__ float smem[];   // [rot_dims / 2][2] cosine, sine; then 33 floats for the sum
     float* cs = smem;
     float* scratch = smem + p.rot_dims;
+    pdl_wait();   // everything in front is complete before anything is read; then the next kernel may be set up meanwhile
+    pdl_launch_dependents();
     const int t = blockIdx.x;
     const int pos = p.token_pos[t];
     const int slot = p.slot_ids[p.token_seq[t]];
@@ -108,6 +110,6 @@ HYMT2_API int hymt2_latent_prep(const void* proj, long ldp, int q_cols, void* q_
     p.table_stride = table_stride; p.block_tokens = block_tokens; p.heads = heads; p.dim = dim; p.rot = rot; p.rank = rank;
     p.rot_dims = rot_dims; p.eps = eps; p.amplitude = amplitude;
     const size_t smem = sizeof(float) * ((size_t)rot_dims + 33);
-    HYMT2_DISPATCH_DTYPE(dtype, T, (latent_prep_kernel<T><<<tokens, 128, smem, stream>>>(p)));
+    HYMT2_DISPATCH_DTYPE(dtype, T, launch_pdl(latent_prep_kernel<T>, dim3(tokens), dim3(128), smem, stream, p));
     return hymt2_check_launch("latent_prep");
 }

@@ -1,0 +1,298 @@
+// bfloat16 attention over a cache of ONE vector per token that all heads share (see hymt2_attention_shared_vector:
+// every head's key is the whole row of width d, every head's value its first dv entries), on the tensor cores through
+// warp-level matrix fragments (16x16x16, float32 accumulation).  Prompts, portions of prompts and decode steps.
+//
+// Because all heads read the same keys, the (token, head) pairs of a sequence are simply the consecutive rows of
+// q [T * heads, d]: a block owns 64 of them and walks the keys in tiles of 64, which is one cache block and therefore
+// one contiguous piece of memory.  Per tile: S = Q K^T into shared memory; the online softmax on S in float32 (the
+// row's running maximum and sum, the factor that the old sums shrink by); P in bfloat16; O = O * factor + P V with
+// O [64, dv] held in accumulator fragments.  How the entries of an accumulator fragment map to rows is found out once,
+// by loading a matrix whose entries are their own row numbers.
+// Row r of sequence b (token r / heads of its new tokens) sits at position p = kv_len - n_b + r / heads and sees the
+// keys max(0, p - window + 1) .. p.  With split_keys > 0 (decode steps) a block takes one chunk of that many keys
+// and leaves unnormalised partials, which the merge kernel of the CUDA-core attention folds in chunk order.
+#include "common.cuh"
+
+#include <mma.h>
+
+int hymt2_attention_merge_launch(void* out, int dtype, const int* cu_seqlens, const int* slot_ids, const int* kv_lens,
+                                 float* part_acc, float* part_ml, int tokens, int nh, int d, int window, int split_keys,
+                                 int max_splits, cudaStream_t stream, int* status);
+
+namespace {
+
+using namespace nvcuda;
+typedef __nv_bfloat16 bf16;
+
+constexpr int MT = 64, NT = 64, THREADS = 256, S_LD = 68, P_LD = 72;
+
+struct LatentMmaParams {
+    const bf16* q;        // [T * nh, d]
+    bf16* out;            // [T * nh, dv]
+    const bf16* cache;    // plane base, [block][64][d]
+    const int* block_table;
+    const int* cu_seqlens;
+    const int* slot_ids;
+    const int* kv_lens;
+    float* part_acc;      // [T * nh, splits, dv]
+    float* part_ml;       // [T * nh, splits, 2]
+    int table_stride, nh, d, dv, window, split_keys, max_splits;
+    float scale;
+};
+
+template <int MAXF>
+__global__ void __launch_bounds__(THREADS, 1)
+latent_attention_mma_kernel(LatentMmaParams p) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const int d = p.d, dv = p.dv, ldq = d + 8;
+    bf16* Qs = reinterpret_cast<bf16*>(smem_raw);           // [64][ldq]
+    bf16* Ks = Qs + MT * ldq;                               // [64][ldq]
+    float* Ss = reinterpret_cast<float*>(Ks + NT * ldq);    // [64][S_LD]
+    bf16* Ps = reinterpret_cast<bf16*>(Ss + MT * S_LD);     // [64][P_LD]
+    float* m_s = reinterpret_cast<float*>(Ps + MT * P_LD);  // [64] running maximum
+    float* l_s = m_s + MT;                                  // [64] running sum
+    float* corr_s = l_s + MT;                               // [64] what the old sums shrink by in this tile
+
+    const int b = blockIdx.z / p.max_splits, split = blockIdx.z % p.max_splits;
+    const int slot = p.slot_ids[b];
+    if (slot < 0) return;
+    const int tok0 = p.cu_seqlens[b], n = p.cu_seqlens[b + 1] - tok0;
+    const int kv_len = p.kv_lens[b], start = kv_len - n;
+    const int rows_total = n * p.nh, r0 = blockIdx.x * MT;
+    if (r0 >= rows_total) return;
+    const int rows_valid = min(MT, rows_total - r0);
+    const int first_tok = r0 / p.nh, last_tok = (r0 + rows_valid - 1) / p.nh;
+    int key_end = start + last_tok + 1;
+    int key_begin = p.window > 0 ? max(0, start + first_tok - p.window + 1) : 0;
+    if (p.split_keys > 0) {
+        key_begin = max(key_begin, split * p.split_keys);
+        key_end = min(key_end, (split + 1) * p.split_keys);
+    }
+    if (key_begin >= key_end) return;   // (no row of this tile sees a key of this chunk; the merge never asks for it)
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const size_t row_base = (size_t)tok0 * p.nh + r0;     // first of this tile's rows among all (token, head) rows
+
+    // the queries
+    const bf16* qg = p.q + row_base * d;
+    for (int i = tid * 8; i < MT * d; i += THREADS * 8) {
+        const int r = i / d, c = i - r * d;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (r < rows_valid) v = *reinterpret_cast<const uint4*>(qg + (size_t)r * d + c);
+        *reinterpret_cast<uint4*>(Qs + r * ldq + c) = v;
+    }
+    if (tid < MT) { m_s[tid] = -INFINITY; l_s[tid] = 0.f; corr_s[tid] = 1.f; }
+
+    // which row of its 16 each entry of an accumulator fragment belongs to
+    const int rf_o = warp & 3, cf_o = warp >> 2;            // this warp's row fragment of O, and its first column fragment
+    float* stage = Ss + rf_o * 16 * S_LD + cf_o * 16;       // a 16x16 float32 patch of S that only this warp touches outside the S phase
+    int row_of[8];
+    {
+        for (int i = lane; i < 256; i += 32) stage[(i >> 4) * S_LD + (i & 15)] = (float)(i >> 4);
+        __syncwarp();
+        wmma::fragment<wmma::accumulator, 16, 16, 16, float> probe;
+        wmma::load_matrix_sync(probe, stage, S_LD, wmma::mem_row_major);
+#pragma unroll
+        for (int e = 0; e < 8; e++) row_of[e] = (int)probe.x[e];
+    }
+    const int o_frags_total = 4 * (dv >> 4);                // fragments of O; this warp owns warp, warp + 8, ...: row fragment rf_o,
+    wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc[MAXF];   // column fragments cf_o, cf_o + 2, ...
+#pragma unroll
+    for (int i = 0; i < MAXF; i++) wmma::fill_fragment(acc[i], 0.f);
+    const bool o_rows_live = rf_o * 16 < rows_valid;
+    const int rf_s = warp >> 1, cf_s = (warp & 1) * 2;      // this warp's part of S: row fragment rf_s, column fragments cf_s, cf_s + 1
+    const bool s_rows_live = rf_s * 16 < rows_valid;
+
+    const int* table = p.block_table + (size_t)slot * p.table_stride;
+    for (int k0 = (key_begin / NT) * NT; k0 < key_end; k0 += NT) {
+        __syncthreads();   // the tile before is done with Ks and Ps (and, first time round, Qs and the statistics are written)
+        const int block = table[k0 / NT];
+        const bf16* kg = p.cache + (size_t)(block < 0 ? 0 : block) * NT * d;
+        const int keys_here = block < 0 ? 0 : min(NT, kv_len - k0);   // rows past the sequence's end hold anything: they are zeroed
+        for (int i = tid * 8; i < NT * d; i += THREADS * 8) {
+            const int r = i / d, c = i - r * d;
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (r < keys_here) v = *reinterpret_cast<const uint4*>(kg + i);
+            *reinterpret_cast<uint4*>(Ks + r * ldq + c) = v;
+        }
+        __syncthreads();
+
+        // S = Q K^T
+        if (s_rows_live) {
+            wmma::fragment<wmma::accumulator, 16, 16, 16, float> s0, s1;
+            wmma::fill_fragment(s0, 0.f);
+            wmma::fill_fragment(s1, 0.f);
+            const bf16* qa = Qs + rf_s * 16 * ldq;
+            const bf16* kb0 = Ks + cf_s * 16 * ldq;
+            const bf16* kb1 = kb0 + 16 * ldq;
+            for (int kk = 0; kk < d; kk += 16) {
+                wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> a;
+                wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::col_major> b0, b1;
+                wmma::load_matrix_sync(a, qa + kk, ldq);
+                wmma::load_matrix_sync(b0, kb0 + kk, ldq);
+                wmma::load_matrix_sync(b1, kb1 + kk, ldq);
+                wmma::mma_sync(s0, a, b0, s0);
+                wmma::mma_sync(s1, a, b1, s1);
+            }
+            wmma::store_matrix_sync(Ss + rf_s * 16 * S_LD + cf_s * 16, s0, S_LD, wmma::mem_row_major);
+            wmma::store_matrix_sync(Ss + rf_s * 16 * S_LD + cf_s * 16 + 16, s1, S_LD, wmma::mem_row_major);
+        }
+        __syncthreads();
+
+        // the online softmax: four threads a row, 16 keys each
+        {
+            const int r = tid >> 2, part = tid & 3;
+            const int grow = r0 + r;
+            const bool row_ok = r < rows_valid;
+            const int pos = start + grow / p.nh;
+            const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+            float s[16];
+            float tmax = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 16; j++) {
+                const int key = k0 + part * 16 + j;
+                const bool visible = row_ok && key >= lo && key <= pos && key >= key_begin && key < key_end;
+                s[j] = visible ? Ss[r * S_LD + part * 16 + j] * p.scale : -INFINITY;
+                tmax = fmaxf(tmax, s[j]);
+            }
+            tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
+            tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
+            const float m_old = m_s[r], m_new = fmaxf(m_old, tmax);
+            float corr = 1.f, psum = 0.f;
+            __nv_bfloat162 pb[8];
+            if (m_new > -INFINITY) {
+                corr = expf(m_old - m_new);
+#pragma unroll
+                for (int j = 0; j < 16; j += 2) {
+                    const float p0 = expf(s[j] - m_new), p1 = expf(s[j + 1] - m_new);
+                    psum += p0 + p1;
+                    pb[j >> 1] = __floats2bfloat162_rn(p0, p1);
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; j++) pb[j] = __floats2bfloat162_rn(0.f, 0.f);
+            }
+            psum += __shfl_xor_sync(0xffffffffu, psum, 1);
+            psum += __shfl_xor_sync(0xffffffffu, psum, 2);
+            uint4* dst = reinterpret_cast<uint4*>(Ps + r * P_LD + part * 16);
+            dst[0] = *reinterpret_cast<uint4*>(&pb[0]);
+            dst[1] = *reinterpret_cast<uint4*>(&pb[4]);
+            __syncwarp();
+            if (part == 0) {
+                m_s[r] = m_new;
+                l_s[r] = l_s[r] * corr + psum;
+                corr_s[r] = corr;
+            }
+        }
+        __syncthreads();
+
+        // O = O * factor + P V (the values are the first dv entries of the key rows)
+        if (o_rows_live) {
+            float f[8];
+#pragma unroll
+            for (int e = 0; e < 8; e++) f[e] = corr_s[rf_o * 16 + row_of[e]];
+#pragma unroll
+            for (int i = 0; i < MAXF; i++)
+                if (warp + 8 * i < o_frags_total) {
+#pragma unroll
+                    for (int e = 0; e < 8; e++) acc[i].x[e] *= f[e];
+                }
+#pragma unroll
+            for (int kk = 0; kk < NT; kk += 16) {
+                wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> a;
+                wmma::load_matrix_sync(a, Ps + rf_o * 16 * P_LD + kk, P_LD);
+#pragma unroll
+                for (int i = 0; i < MAXF; i++)
+                    if (warp + 8 * i < o_frags_total) {
+                        wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::row_major> vb;
+                        wmma::load_matrix_sync(vb, Ks + kk * ldq + (cf_o + 2 * i) * 16, ldq);
+                        wmma::mma_sync(acc[i], a, vb, acc[i]);
+                    }
+            }
+        }
+    }
+    __syncthreads();
+
+    const bool split_mode = p.split_keys > 0;
+    if (split_mode && tid < rows_valid) {
+        float* ml = p.part_ml + ((row_base + tid) * p.max_splits + split) * 2;
+        ml[0] = m_s[tid];
+        ml[1] = l_s[tid];
+    }
+    if (!o_rows_live) return;
+    float f[8];
+#pragma unroll
+    for (int e = 0; e < 8; e++) {
+        const float l = l_s[rf_o * 16 + row_of[e]];
+        f[e] = split_mode ? 1.f : (l > 0.f ? 1.0f / l : 0.f);
+    }
+#pragma unroll
+    for (int i = 0; i < MAXF; i++) {
+        if (warp + 8 * i >= o_frags_total) continue;
+#pragma unroll
+        for (int e = 0; e < 8; e++) acc[i].x[e] *= f[e];
+        wmma::store_matrix_sync(stage, acc[i], S_LD, wmma::mem_row_major);
+        __syncwarp();
+        const int r = lane >> 1, c8 = (lane & 1) * 8;
+        const int row = rf_o * 16 + r, col = (cf_o + 2 * i) * 16 + c8;
+        if (row < rows_valid) {
+            const float* src = stage + r * S_LD + c8;
+            if (split_mode) {
+                float* dst = p.part_acc + ((row_base + row) * p.max_splits + split) * dv + col;
+#pragma unroll
+                for (int e = 0; e < 8; e++) dst[e] = src[e];
+            } else {
+                __nv_bfloat162 h[4];
+#pragma unroll
+                for (int e = 0; e < 4; e++) h[e] = __floats2bfloat162_rn(src[2 * e], src[2 * e + 1]);
+                *reinterpret_cast<uint4*>(p.out + (row_base + row) * dv + col) = *reinterpret_cast<uint4*>(h);
+            }
+        }
+        __syncwarp();
+    }
+}
+
+size_t smem_bytes(int d) {
+    return (size_t)2 * MT * (d + 8) * sizeof(bf16) + (size_t)MT * S_LD * sizeof(float) + (size_t)MT * P_LD * sizeof(bf16) + 3 * MT * sizeof(float);
+}
+
+}  // namespace
+
+// Whether the kernel takes these sizes: rows of 16-element pieces, cache blocks of 64 tokens, and room in shared memory.
+HYMT2_API int hymt2_latent_attention_mma_supported(int d, int dv, int block_tokens) {
+    return d > 0 && dv > 0 && d % 16 == 0 && dv % 16 == 0 && dv <= d && dv <= 512 && block_tokens == NT && smem_bytes(d) <= 220 * 1024;
+}
+
+HYMT2_API int hymt2_latent_attention_mma(void* out, const void* q, const void* cache, const int* block_table, int table_stride,
+                                         int block_tokens, const int* cu_seqlens, const int* slot_ids, const int* kv_lens, int batch,
+                                         int tokens, int max_new_tokens, int nh, int d, int dv, float scale, int window,
+                                         int split_keys, int max_splits, float* part_acc, float* part_ml, int* status,
+                                         cudaStream_t stream) {
+    if (batch == 0 || tokens == 0) return HYMT2_OK;
+    HYMT2_REQUIRE(hymt2_latent_attention_mma_supported(d, dv, block_tokens), "latent_attention_mma: keys of %d, values of %d, blocks of %d are not taken", d, dv, block_tokens);
+    HYMT2_REQUIRE(batch > 0 && tokens > 0 && nh > 0 && max_new_tokens > 0, "latent_attention_mma: bad sizes");
+    HYMT2_REQUIRE((uintptr_t)q % 16 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)cache % 16 == 0, "latent_attention_mma: operands must be 16-byte aligned");
+    HYMT2_REQUIRE(split_keys == 0 || (split_keys % NT == 0 && max_splits > 0 && part_acc && part_ml), "latent_attention_mma: a split comes in whole tiles and with scratch");
+    LatentMmaParams p;
+    p.q = (const bf16*)q; p.out = (bf16*)out; p.cache = (const bf16*)cache; p.block_table = block_table; p.cu_seqlens = cu_seqlens;
+    p.slot_ids = slot_ids; p.kv_lens = kv_lens; p.part_acc = part_acc; p.part_ml = part_ml; p.table_stride = table_stride; p.nh = nh;
+    p.d = d; p.dv = dv; p.window = window; p.split_keys = split_keys; p.max_splits = split_keys > 0 ? max_splits : 1; p.scale = scale;
+    const long row_tiles = ((long)max_new_tokens * nh + MT - 1) / MT;
+    HYMT2_REQUIRE(row_tiles <= 2147483647L && (long)batch * p.max_splits <= 65535, "latent_attention_mma: grid too large");
+    const dim3 grid((unsigned)row_tiles, 1, (unsigned)(batch * p.max_splits));
+    const size_t smem = smem_bytes(d);
+    auto launch = [&](auto kernel) -> int {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) { hymt2_set_error("latent_attention_mma: %s", cudaGetErrorString(e)); return HYMT2_ERR_LAUNCH; }
+        kernel<<<grid, THREADS, smem, stream>>>(p);
+        return hymt2_check_launch("latent_attention_mma");
+    };
+    int rc;
+    if (dv <= 128) rc = launch(latent_attention_mma_kernel<4>);
+    else if (dv <= 256) rc = launch(latent_attention_mma_kernel<8>);
+    else rc = launch(latent_attention_mma_kernel<16>);
+    if (rc == HYMT2_OK && split_keys > 0)
+        rc = hymt2_attention_merge_launch(out, HYMT2_BF16, cu_seqlens, slot_ids, kv_lens, part_acc, part_ml, tokens, nh, dv, window,
+                                          split_keys, max_splits, stream, status);
+    return rc;
+}

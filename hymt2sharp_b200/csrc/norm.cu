@@ -84,6 +84,8 @@ template <typename TX, typename TW, typename TY, bool ADD>
 __global__ void rmsnorm_groups_kernel(TY* __restrict__ y, const TX* __restrict__ x, const TW* __restrict__ gain,
                                       const int* __restrict__ rows_index, int dim, int part, float eps, float out_scale) {
     __shared__ float scratch[33];
+    pdl_wait();   // everything in front is complete before anything is read; then the next kernel may be set up meanwhile
+    pdl_launch_dependents();
     const int r = blockIdx.x, g = blockIdx.y;
     const TX* src = x + (size_t)(rows_index ? rows_index[r] : r) * dim + (size_t)g * part;
     float ss = 0.f;
@@ -115,10 +117,10 @@ HYMT2_API int hymt2_rmsnorm_groups(void* y, int y_dtype, const void* x, int x_dt
     const dim3 grid(rows, groups);
     HYMT2_DISPATCH_DTYPE(x_dtype, TX, HYMT2_DISPATCH_DTYPE(gain_dtype, TW, {
         if (add) {
-            rmsnorm_groups_kernel<TX, TW, float, true><<<grid, threads, 0, stream>>>((float*)y, (const TX*)x, (const TW*)gain,
-                                                                                    rows_index, dim, part, eps, out_scale);
+            launch_pdl(rmsnorm_groups_kernel<TX, TW, float, true>, grid, dim3(threads), 0, stream, (float*)y, (const TX*)x, (const TW*)gain,
+                       rows_index, dim, part, eps, out_scale);
         } else {
-            HYMT2_DISPATCH_DTYPE(y_dtype, TY, (rmsnorm_groups_kernel<TX, TW, TY, false><<<grid, threads, 0, stream>>>(
+            HYMT2_DISPATCH_DTYPE(y_dtype, TY, (launch_pdl(rmsnorm_groups_kernel<TX, TW, TY, false>, grid, dim3(threads), 0, stream,
                 (TY*)y, (const TX*)x, (const TW*)gain, rows_index, dim, part, eps, out_scale)));
         }
     }));

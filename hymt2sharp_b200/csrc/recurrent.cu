@@ -29,6 +29,8 @@ struct ConvParams {
 template <typename T>
 __global__ void __launch_bounds__(CONV_THREADS)
 causal_conv_kernel(ConvParams p) {
+    pdl_wait();   // everything in front is complete before anything is read; then the next kernel may be set up meanwhile
+    pdl_launch_dependents();
     const int c = blockIdx.x * CONV_THREADS + threadIdx.x;
     const int b = blockIdx.z;
     if (c >= p.channels) return;
@@ -120,52 +122,107 @@ struct ScanParams {
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf(-x)); }
 
-template <typename T>
-__global__ void __launch_bounds__(RG_THREADS)
-rglru_scan_kernel(ScanParams p) {
-    const int c = blockIdx.x * RG_THREADS + threadIdx.x;
-    const int b = blockIdx.y;
-    if (c >= p.width) return;
-    const int tok0 = p.cu_seqlens[b], n = p.cu_seqlens[b + 1] - tok0;
-    const int slot = p.slot_ids[b];
-    T* out = (T*)p.out + (size_t)tok0 * p.ldo + c;
-    if (slot < 0) {
-        for (int i = 0; i < n; i++) out[(size_t)i * p.ldo] = from_float<T>(0.f);
-        return;
-    }
-    const int start = p.kv_lens[b] - n;
-    float* st = (float*)(p.state + (size_t)slot * p.state_stride) + c;
-    float S = start > 0 ? *st : 0.f;
+// Walks tokens [i_begin, i_end) of one sequence's channel c from the state S; returns the new S.  WRITE: the outputs
+// S * y are stored; otherwise only the state moves (and *prod collects the product of the decays on the way).
+template <typename T, bool WRITE>
+__device__ __forceinline__ float rglru_walk(const ScanParams& p, int c, int tok0, int i_begin, int i_end, float S, float* prod) {
     const float br = p.br[c], bi = p.bi[c];
     const float rate = -p.decay * softplus_f(p.lam[c]);
     const float* gates = p.gates + (size_t)tok0 * 2 * p.width + c;
     const T* u = (const T*)p.u + (size_t)tok0 * p.ldu + c;
     const T* y = (const T*)p.y + (size_t)tok0 * p.ldy + c;
-    for (int i0 = 0; i0 < n; i0 += RG_BATCH) {
+    T* out = (T*)p.out + (size_t)tok0 * p.ldo + c;
+    float A = 1.f;
+    for (int i0 = i_begin; i0 < i_end; i0 += RG_BATCH) {
         float a[RG_BATCH], bx[RG_BATCH], yy[RG_BATCH];
 #pragma unroll
         for (int k = 0; k < RG_BATCH; k++) {
             const int i = i0 + k;
             a[k] = 1.f; bx[k] = 0.f; yy[k] = 0.f;
-            if (i < n) {
+            if (i < i_end) {
                 const float r = sigmoid_f(gates[(size_t)i * 2 * p.width] + br);
                 const float g = sigmoid_f(gates[(size_t)i * 2 * p.width + p.width] + bi);
                 const float log_a = rate * r;
                 a[k] = expf(log_a);
                 bx[k] = sqrtf(-expm1f(2.f * log_a)) * g * to_float(u[(size_t)i * p.ldu]);
-                yy[k] = to_float(y[(size_t)i * p.ldy]);
+                if (WRITE) yy[k] = to_float(y[(size_t)i * p.ldy]);
             }
         }
 #pragma unroll
         for (int k = 0; k < RG_BATCH; k++) {
             const int i = i0 + k;
-            if (i < n) {
+            if (i < i_end) {
                 S = fmaf(a[k], S, bx[k]);
-                out[(size_t)i * p.ldo] = from_float<T>(S * yy[k]);
+                A *= a[k];
+                if (WRITE) out[(size_t)i * p.ldo] = from_float<T>(S * yy[k]);
             }
         }
     }
-    *st = S;
+    if (prod) *prod = A;
+    return S;
+}
+
+// One thread walks ALL new tokens of its sequence's channel: decode steps and short portions.
+template <typename T>
+__global__ void __launch_bounds__(RG_THREADS)
+rglru_scan_kernel(ScanParams p) {
+    pdl_wait();   // everything in front is complete before anything is read; then the next kernel may be set up meanwhile
+    pdl_launch_dependents();
+    const int c = blockIdx.x * RG_THREADS + threadIdx.x;
+    const int b = blockIdx.y;
+    if (c >= p.width) return;
+    const int tok0 = p.cu_seqlens[b], n = p.cu_seqlens[b + 1] - tok0;
+    const int slot = p.slot_ids[b];
+    if (slot < 0) {
+        T* out = (T*)p.out + (size_t)tok0 * p.ldo + c;
+        for (int i = 0; i < n; i++) out[(size_t)i * p.ldo] = from_float<T>(0.f);
+        return;
+    }
+    const int start = p.kv_lens[b] - n;
+    float* st = (float*)(p.state + (size_t)slot * p.state_stride) + c;
+    *st = rglru_walk<T, true>(p, c, tok0, 0, n, start > 0 ? *st : 0.f, nullptr);
+}
+
+// Long portions in two passes over chunks of RG_CHUNK tokens.  The recurrence S <- a S + b composes: a chunk as a whole
+// is S_out = A * S_in + B with A the product of its decays and B what it leaves from a zero state.  Pass 1: every
+// (chunk, channel) thread finds its (A, B); the threads of chunk 0 also note the state that the sequence came with.
+// Pass 2: every thread folds the (A, B) of the chunks before its own, in order, into its S_in, walks its chunk again
+// and writes the outputs; the last chunk's thread leaves the new state.
+// scratch: [batch][chunks + 1][2][width] floats; entry `chunks` holds the incoming state.
+constexpr int RG_CHUNK = 64;
+
+template <typename T, int PASS>
+__global__ void __launch_bounds__(RG_THREADS)
+rglru_chunk_kernel(ScanParams p, float* scratch, int chunks) {
+    const int c = blockIdx.x * RG_THREADS + threadIdx.x;
+    const int k = blockIdx.y, b = blockIdx.z;
+    if (c >= p.width) return;
+    const int tok0 = p.cu_seqlens[b], n = p.cu_seqlens[b + 1] - tok0;
+    const int i0 = k * RG_CHUNK;
+    if (i0 >= n) return;
+    const int i1 = min(n, i0 + RG_CHUNK);
+    const int slot = p.slot_ids[b];
+    float* mine = scratch + ((size_t)b * (chunks + 1)) * 2 * p.width + c;
+    if (slot < 0) {
+        if (PASS == 2) {
+            T* out = (T*)p.out + (size_t)tok0 * p.ldo + c;
+            for (int i = i0; i < i1; i++) out[(size_t)i * p.ldo] = from_float<T>(0.f);
+        }
+        return;
+    }
+    float* st = (float*)(p.state + (size_t)slot * p.state_stride) + c;
+    if (PASS == 1) {
+        float A;
+        const float B = rglru_walk<T, false>(p, c, tok0, i0, i1, 0.f, &A);
+        mine[(size_t)k * 2 * p.width] = A;
+        mine[(size_t)k * 2 * p.width + p.width] = B;
+        if (k == 0) mine[(size_t)chunks * 2 * p.width] = p.kv_lens[b] - n > 0 ? *st : 0.f;
+    } else {
+        float S = mine[(size_t)chunks * 2 * p.width];
+        for (int j = 0; j < k; j++) S = fmaf(mine[(size_t)j * 2 * p.width], S, mine[(size_t)j * 2 * p.width + p.width]);
+        S = rglru_walk<T, true>(p, c, tok0, i0, i1, S, nullptr);
+        if (i1 == n) *st = S;
+    }
 }
 
 }  // namespace
@@ -186,14 +243,22 @@ HYMT2_API int hymt2_causal_conv(void* out, const void* x, int dtype, const float
     const int chunks = (max_new_tokens + CONV_CHUNK - 1) / CONV_CHUNK;
     HYMT2_REQUIRE(chunks <= 65535, "causal_conv: %d tokens in one sequence are too many for one launch", max_new_tokens);
     const dim3 grid((channels + CONV_THREADS - 1) / CONV_THREADS, chunks, batch);
-    HYMT2_DISPATCH_DTYPE(dtype, T, (causal_conv_kernel<T><<<grid, CONV_THREADS, 0, stream>>>(p)));
+    HYMT2_DISPATCH_DTYPE(dtype, T, launch_pdl(causal_conv_kernel<T>, grid, dim3(CONV_THREADS), 0, stream, p));
     return hymt2_check_launch("causal_conv");
+}
+
+// Floats of scratch that a step whose longest portion has max_new_tokens tokens needs (0: one pass, no scratch).
+HYMT2_API long hymt2_rglru_scan_scratch(int batch, int max_new_tokens, int width) {
+    if (max_new_tokens <= 2 * RG_CHUNK) return 0;
+    const long chunks = (max_new_tokens + RG_CHUNK - 1) / RG_CHUNK;
+    return (long)batch * (chunks + 1) * 2 * width;
 }
 
 HYMT2_API int hymt2_rglru_scan(void* out, const float* gates, const void* u, const void* y, int dtype, const float* br,
                                const float* bi, const float* lam, float decay, void* state, long state_offset,
                                long state_stride, const int* cu_seqlens, const int* slot_ids, const int* kv_lens, int batch,
-                               int width, int ldu, int ldy, int ldo, cudaStream_t stream) {
+                               int width, int ldu, int ldy, int ldo, int max_new_tokens, float* scratch, long scratch_floats,
+                               cudaStream_t stream) {
     if (batch == 0) return HYMT2_OK;
     HYMT2_REQUIRE(batch > 0 && batch <= 65535 && width > 0, "rglru_scan: bad sizes");
     HYMT2_REQUIRE(state_offset % 4 == 0 && state_stride % 4 == 0, "rglru_scan: the state must be 4-byte aligned");
@@ -202,7 +267,19 @@ HYMT2_API int hymt2_rglru_scan(void* out, const float* gates, const void* u, con
     p.state = (uint8_t*)state + state_offset; p.state_stride = state_stride;
     p.cu_seqlens = cu_seqlens; p.slot_ids = slot_ids; p.kv_lens = kv_lens;
     p.width = width; p.ldu = ldu; p.ldy = ldy; p.ldo = ldo; p.decay = decay;
+    const long need = hymt2_rglru_scan_scratch(batch, max_new_tokens, width);
+    if (need > 0) {
+        HYMT2_REQUIRE(scratch != nullptr && scratch_floats >= need, "rglru_scan: %ld floats of scratch are needed", need);
+        const int chunks = (max_new_tokens + RG_CHUNK - 1) / RG_CHUNK;
+        HYMT2_REQUIRE(chunks <= 65535, "rglru_scan: %d tokens in one portion are too many", max_new_tokens);
+        const dim3 grid((width + RG_THREADS - 1) / RG_THREADS, chunks, batch);
+        HYMT2_DISPATCH_DTYPE(dtype, T, {
+            rglru_chunk_kernel<T, 1><<<grid, RG_THREADS, 0, stream>>>(p, scratch, chunks);
+            rglru_chunk_kernel<T, 2><<<grid, RG_THREADS, 0, stream>>>(p, scratch, chunks);
+        });
+        return hymt2_check_launch("rglru_scan");
+    }
     const dim3 grid((width + RG_THREADS - 1) / RG_THREADS, batch);
-    HYMT2_DISPATCH_DTYPE(dtype, T, (rglru_scan_kernel<T><<<grid, RG_THREADS, 0, stream>>>(p)));
+    HYMT2_DISPATCH_DTYPE(dtype, T, launch_pdl(rglru_scan_kernel<T>, grid, dim3(RG_THREADS), 0, stream, p));
     return hymt2_check_launch("rglru_scan");
 }

@@ -861,10 +861,11 @@ def causal_conv(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, bias: torch
 
 def rglru_scan(out: torch.Tensor, gates: torch.Tensor, u: torch.Tensor, y: torch.Tensor, br: torch.Tensor, bi: torch.Tensor,
                lam: torch.Tensor, decay: float, state: torch.Tensor, state_offset: int, cu_seqlens: torch.Tensor,
-               slot_ids: torch.Tensor, kv_lens: torch.Tensor, batch: int) -> None:
+               slot_ids: torch.Tensor, kv_lens: torch.Tensor, batch: int, max_new_tokens: int) -> None:
     """The real-gated linear recurrence over every sequence's new tokens, in float32: r = sigmoid(gates[:, :W] + br),
     i = sigmoid(gates[:, W:] + bi), a = exp(-decay * r * softplus(lam)), S <- a S + sqrt(1 - a^2) i u, out = S * y.
-    S (float32 [W]) lies at byte `state_offset` of the sequence's state row."""
+    S (float32 [W]) lies at byte `state_offset` of the sequence's state row.  Portions longer than two chunks of 64 tokens
+    run in two passes over chunks (the recurrence composes), every chunk a thread of its own per channel."""
     T, W = u.shape
     ldu, ldy, ldo = _rows_view(u, "u"), _rows_view(y, "y", u.dtype), _rows_view(out, "out", u.dtype)
     _need(gates, "gates", torch.float32, 2)
@@ -875,10 +876,14 @@ def rglru_scan(out: torch.Tensor, gates: torch.Tensor, u: torch.Tensor, y: torch
         raise KernelError("rglru_scan: the state rows are too short")
     for t, n in ((cu_seqlens, "cu_seqlens"), (slot_ids, "slot_ids"), (kv_lens, "kv_lens")):
         _need(t, n, torch.int32, 1)
-    _check(_lib().hymt2_rglru_scan(_ptr(out), _ptr(gates), _ptr(u), _ptr(y), c_int(dtype_code(u.dtype)), _ptr(br), _ptr(bi), _ptr(lam),
-                                   c_float(decay), _ptr(state), c_long(state_offset), c_long(state.stride(0)), _ptr(cu_seqlens),
-                                   _ptr(slot_ids), _ptr(kv_lens), c_int(batch), c_int(W), c_int(ldu), c_int(ldy), c_int(ldo),
-                                   _stream()), "rglru_scan")
+    lib = _lib()
+    lib.hymt2_rglru_scan_scratch.restype = c_long
+    floats = int(lib.hymt2_rglru_scan_scratch(c_int(batch), c_int(max_new_tokens), c_int(W)))
+    scratch = torch.empty(floats, dtype=torch.float32, device=u.device) if floats else None
+    _check(lib.hymt2_rglru_scan(_ptr(out), _ptr(gates), _ptr(u), _ptr(y), c_int(dtype_code(u.dtype)), _ptr(br), _ptr(bi), _ptr(lam),
+                                c_float(decay), _ptr(state), c_long(state_offset), c_long(state.stride(0)), _ptr(cu_seqlens),
+                                _ptr(slot_ids), _ptr(kv_lens), c_int(batch), c_int(W), c_int(ldu), c_int(ldy), c_int(ldo),
+                                c_int(max_new_tokens), _ptr(scratch), c_long(floats), _stream()), "rglru_scan", 2 if floats else 1)
 
 
 def bias_act(x: torch.Tensor, bias: torch.Tensor | None, act_cols: int) -> None:
@@ -985,3 +990,60 @@ def attention_shared_vector(out: torch.Tensor, q: torch.Tensor, cache_plane: tor
                                                 c_int(nh), c_int(d), c_int(dv), c_float(scale), c_int(window), c_int(split_keys),
                                                 c_int(max_splits), _ptr(part_acc), _ptr(part_ml), _stream(), _ptr(status)),
            "attention_shared_vector", 2 if split_keys > 0 else 1)
+
+
+_mma_ok: dict = {}
+
+
+def latent_attention_mma_supported(dtype: torch.dtype, d: int, dv: int, block_tokens: int) -> bool:
+    """Whether the tensor-core kernel of the shared-vector attention takes these sizes (bfloat16, rows in pieces of 16)."""
+    if dtype != torch.bfloat16:
+        return False
+    key = (d, dv, block_tokens)
+    hit = _mma_ok.get(key)
+    if hit is None:
+        hit = _mma_ok[key] = bool(_lib().hymt2_latent_attention_mma_supported(c_int(d), c_int(dv), c_int(block_tokens)))
+    return hit
+
+
+def latent_attention_mma(out: torch.Tensor, q: torch.Tensor, cache_plane: torch.Tensor, block_table: torch.Tensor,
+                         cu_seqlens: torch.Tensor, slot_ids: torch.Tensor, kv_lens: torch.Tensor, batch: int, max_new_tokens: int,
+                         nh: int, d: int, dv: int, scale: float, window: int = 0, split_keys: int = 0, max_splits: int = 0,
+                         part_acc: torch.Tensor | None = None, part_ml: torch.Tensor | None = None,
+                         status: torch.Tensor | None = None) -> None:
+    """attention_shared_vector in bfloat16 on the tensor cores (16x16x16 fragments, float32 sums and softmax): the same
+    arguments and the same partials when split."""
+    if status is None:
+        status = device_status(out.device)
+    _need(out, "out", torch.bfloat16, 2); _need(q, "q", torch.bfloat16, 2); _need(cache_plane, "cache_plane", torch.bfloat16, 4)
+    T = out.shape[0]
+    if out.shape[1] != nh * dv or q.shape != (T, nh * d) or cache_plane.shape[1] != 1 or cache_plane.shape[3] != d:
+        raise KernelError(f"latent_attention_mma: shapes out {tuple(out.shape)} q {tuple(q.shape)} cache {tuple(cache_plane.shape)}")
+    _need(block_table, "block_table", torch.int32, 2)
+    for t, n in ((cu_seqlens, "cu_seqlens"), (slot_ids, "slot_ids"), (kv_lens, "kv_lens")):
+        _need(t, n, torch.int32, 1)
+    if split_keys > 0:
+        _need(part_acc, "part_acc", torch.float32); _need(part_ml, "part_ml", torch.float32)
+        if part_acc.numel() < T * nh * max_splits * dv or part_ml.numel() < T * nh * max_splits * 2:
+            raise KernelError("latent_attention_mma: the split scratch is too small")
+    _check(_lib().hymt2_latent_attention_mma(_ptr(out), _ptr(q), _ptr(cache_plane), _ptr(block_table), c_int(block_table.stride(0)),
+                                             c_int(cache_plane.shape[2]), _ptr(cu_seqlens), _ptr(slot_ids), _ptr(kv_lens), c_int(batch),
+                                             c_int(T), c_int(max_new_tokens), c_int(nh), c_int(d), c_int(dv), c_float(scale),
+                                             c_int(window), c_int(split_keys), c_int(max_splits), _ptr(part_acc), _ptr(part_ml),
+                                             _ptr(status), _stream()), "latent_attention_mma", 2 if split_keys > 0 else 1)
+
+
+SKINNY_MAX_ROWS = 16
+
+
+def gemm_skinny_batched(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, a_step: int, out_step: int) -> None:
+    """gemm_simt_batched for at most 16 rows (a decode step): one warp per output column, the weights read once.
+    a and w have one type; out may be float32."""
+    lda, ldc = _rows_view(a, "a"), _rows_view(out, "out")
+    _need(w, "w", a.dtype, 3)
+    batch, N, K = w.shape
+    if a.shape[0] != out.shape[0] or a.shape[0] > SKINNY_MAX_ROWS or (batch - 1) * a_step + K > a.shape[1] or (batch - 1) * out_step + N > out.shape[1]:
+        raise KernelError(f"gemm_skinny_batched: shapes out {tuple(out.shape)} a {tuple(a.shape)} w {tuple(w.shape)}")
+    _check(_lib().hymt2_gemm_skinny_batched(_ptr(out), c_int(dtype_code(out.dtype)), _ptr(a), _ptr(w), c_int(dtype_code(a.dtype)),
+                                            c_int(a.shape[0]), c_int(N), c_int(K), c_long(lda), c_long(ldc), c_int(batch),
+                                            c_long(a_step), c_long(N * K), c_long(out_step), _stream()), "gemm_skinny_batched")

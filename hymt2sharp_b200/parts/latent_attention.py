@@ -20,9 +20,10 @@ from ..cache.allocator import GroupSpec
 from ..kernels import ops
 from ..weights.loader import TensorSpec
 from .base import MixerSlot, PartSpec, build_part, register_part
-from .linear import Linear, compute_form
+from .linear import Linear, compute_form, matmul_batched
 
-SPLIT_KEYS = 256  # decode: keys per partial, a constant so that the cut depends on nothing else
+SPLIT_KEYS = 256     # decode: keys per partial, a constant so that the cut depends on nothing else
+SPLIT_KEYS_TC = 128  # the same for the tensor-core kernel, whose blocks are few and large: more of them per sequence
 
 
 class LatentAttention:
@@ -91,13 +92,13 @@ class LatentAttention:
                         self.rot, self.rank)
         # q[t, h, :kv_rank] = W_uk[h]^T q_h[:dim]
         ops.tag = "q_absorb"
-        ops.gemm_simt_batched(q, proj, self.uk_t, H, self.dim + self.rot, dl)
+        matmul_batched(q, proj, self.uk_t, self.dim + self.rot, dl)
         ops.tag = None
         mixed = torch.empty((T, H * self.rank), dtype=q.dtype, device=q.device)
         self.attend(mixed, q, plane, table, ctx)
         out = torch.empty((T, H * self.vdim), dtype=q.dtype, device=q.device)
         ops.tag = "v_up"
-        ops.gemm_simt_batched(out, mixed, self.uv, H, self.rank, self.vdim)
+        matmul_batched(out, mixed, self.uv, self.rank, self.vdim)
         ops.tag = None
         if self.gate is not None:
             g0 = self.q_cols + dl
@@ -105,15 +106,18 @@ class LatentAttention:
         self.out.add_then_norm(out, residual, getattr(ctx, "norm_ahead", None), ctx)
 
     def attend(self, out, q, plane, table, ctx) -> None:
+        # bfloat16 with rows in pieces of 16: the tensor-core kernel; 32-bit and odd sizes: the general CUDA-core kernel
+        run, keys = ops.attention_shared_vector, SPLIT_KEYS
+        if ops.latent_attention_mma_supported(out.dtype, self.rank + self.rot, self.rank, plane.shape[2]):
+            run, keys = ops.latent_attention_mma, SPLIT_KEYS_TC
         split, max_splits, acc, ml = 0, 0, None, None
-        if ctx.decode and ctx.max_kv_len > SPLIT_KEYS:
-            split = SPLIT_KEYS
-            max_splits = -(-ctx.max_kv_len // SPLIT_KEYS)
+        if ctx.decode and ctx.max_kv_len > keys:
+            split = keys
+            max_splits = -(-ctx.max_kv_len // keys)
             acc = torch.empty(ctx.num_tokens * self.heads * max_splits * self.rank, dtype=torch.float32, device=out.device)
             ml = torch.empty(ctx.num_tokens * self.heads * max_splits * 2, dtype=torch.float32, device=out.device)
-        ops.attention_shared_vector(out, q, plane, table, ctx.cu_seqlens, ctx.slot_ids, ctx.kv_lens, ctx.num_seqs,
-                                    ctx.max_new_tokens, self.heads, self.rank + self.rot, self.rank, self.scale, self.window,
-                                    split, max_splits, acc, ml)
+        run(out, q, plane, table, ctx.cu_seqlens, ctx.slot_ids, ctx.kv_lens, ctx.num_seqs, ctx.max_new_tokens, self.heads,
+            self.rank + self.rot, self.rank, self.scale, self.window, split, max_splits, acc, ml)
 
 
 register_part("mixer", "latent_attention", LatentAttention)

@@ -67,6 +67,27 @@ class Linear:
         self(x, out=residual)
 
 
+TC_BATCH_MIN_TOKENS = 128   # from this many tokens on, a batch of small products goes to the tensor cores one by one
+
+
+def matmul_batched(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, x_step: int, out_step: int) -> None:
+    """out[:, z*out_step : +N] = x[:, z*x_step : +K] @ w[z]^T for every z of w [batch, N, K]: the per-head or per-block
+    products of a layer (a block-diagonal gate; a projection that every head has of its own).  Few tokens (a decode step):
+    one CUDA-core launch for the whole batch, a warp per output column, which reads w once.  Many tokens: one tensor-core
+    product per z where the kernel takes the operands.  Between the two: one CUDA-core launch in tiles."""
+    batch, N, K = w.shape
+    if x.shape[0] <= ops.SKINNY_MAX_ROWS and x.dtype == w.dtype:
+        ops.gemm_skinny_batched(out, x, w, x_step, out_step)
+        return
+    if x.shape[0] >= TC_BATCH_MIN_TOKENS and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
+        views = [(out[:, z * out_step: z * out_step + N], x[:, z * x_step: z * x_step + K], w[z]) for z in range(batch)]
+        if all(ops.gemm_tc_supported(o, a, b, ops.EPILOGUE_STORE) for o, a, b in views[:2]) and (x_step * 2) % 16 == 0:
+            for o, a, b in views:
+                ops.gemm_tc(o, a, b, ops.EPILOGUE_STORE, ops.device_status(o.device), checked=True)
+            return
+    ops.gemm_simt_batched(out, x, w, batch, x_step, out_step)
+
+
 def matmul(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, epilogue: int) -> None:
     """Picks the kernel: tensor-core kernels where they take the shape and types, else CUDA cores."""
     if fast.try_matmul(out, x, w, epilogue):

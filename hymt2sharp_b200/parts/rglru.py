@@ -18,7 +18,7 @@ from ..kernels import ops
 from ..weights.loader import TensorSpec
 from .base import MixerSlot, register_part
 from .conv import ShortConv
-from .linear import Linear, compute_form
+from .linear import Linear, compute_form, matmul_batched
 
 
 class RGLRU:
@@ -69,12 +69,12 @@ class RGLRU:
         u = self.conv.forward(yx[:, W:], ctx, conv_slot)
         gates = torch.empty((T, 2 * W), dtype=torch.float32, device=u.device)
         ops.tag = "gates"
-        ops.gemm_simt_batched(gates[:, :W], u, self.ra, B, bw, bw)
-        ops.gemm_simt_batched(gates[:, W:], u, self.ia, B, bw, bw)
+        matmul_batched(gates[:, :W], u, self.ra, bw, bw)
+        matmul_batched(gates[:, W:], u, self.ia, bw, bw)
         ops.tag = None
         mixed = torch.empty((T, W), dtype=u.dtype, device=u.device)
         ops.rglru_scan(mixed, gates, u, yx[:, :W], self.rb, self.ib, self.lam, self.decay, ctx.cache.state, slot.state_offset,
-                       ctx.cu_seqlens, ctx.slot_ids, ctx.kv_lens, ctx.num_seqs)
+                       ctx.cu_seqlens, ctx.slot_ids, ctx.kv_lens, ctx.num_seqs, ctx.max_new_tokens)
         self.out.add_then_norm(mixed, residual, getattr(ctx, "norm_ahead", None), ctx)
 
 
