@@ -10,48 +10,87 @@ __device__ __forceinline__ float gelu_tanh_f(float z) {
     return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
 
+// V neighbouring elements in one access of V * sizeof(T) bytes (the caller has checked the alignment).
+template <typename T, int V> struct Pack { T v[V]; };
+template <typename T, int V> __device__ __forceinline__ Pack<T, V> load_pack(const T* p) {
+    Pack<T, V> r;
+    if constexpr (V * sizeof(T) == 16) *reinterpret_cast<uint4*>(r.v) = *reinterpret_cast<const uint4*>(p);
+    else if constexpr (V * sizeof(T) == 8) *reinterpret_cast<uint2*>(r.v) = *reinterpret_cast<const uint2*>(p);
+    else {
+#pragma unroll
+        for (int i = 0; i < V; i++) r.v[i] = p[i];
+    }
+    return r;
+}
+template <typename T, int V> __device__ __forceinline__ void store_pack(T* p, const Pack<T, V>& r) {
+    if constexpr (V * sizeof(T) == 16) *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(r.v);
+    else if constexpr (V * sizeof(T) == 8) *reinterpret_cast<uint2*>(p) = *reinterpret_cast<const uint2*>(r.v);
+    else {
+#pragma unroll
+        for (int i = 0; i < V; i++) p[i] = r.v[i];
+    }
+}
+
 // x[r, c] <- act(x[r, c] + bias[c]); the first `act_cols` columns get the tanh form of GELU, the others the bias alone.
-template <typename T>
+// A thread takes V neighbouring columns (cols is a multiple of V).
+template <typename T, int V>
 __global__ void bias_act_kernel(T* __restrict__ x, const float* __restrict__ bias, int cols, long ld, int act_cols, size_t total) {
     pdl_wait();   // everything in front is complete before anything is read; then the next kernel may be set up meanwhile
     pdl_launch_dependents();
-    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * V;
     if (i >= total) return;
     const size_t r = i / cols;
     const int c = (int)(i - r * cols);
     T* px = x + r * ld + c;
-    float v = to_float(*px) + (bias ? bias[c] : 0.f);
-    if (c < act_cols) v = gelu_tanh_f(v);
-    *px = from_float<T>(v);
+    Pack<T, V> pk = load_pack<T, V>(px);
+#pragma unroll
+    for (int k = 0; k < V; k++) {
+        float v = to_float(pk.v[k]) + (bias ? bias[c + k] : 0.f);
+        if (c + k < act_cols) v = gelu_tanh_f(v);
+        pk.v[k] = from_float<T>(v);
+    }
+    store_pack<T, V>(px, pk);
 }
 
 // xIELU with its two numbers (p, q) read from the device: for z > 0  softplus(p) z^2 + z / 2;
 // for z <= 0  (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2.
-template <typename T>
+template <typename T, int V>
 __global__ void xielu_kernel(T* __restrict__ out, const T* __restrict__ x, const float* __restrict__ pq, size_t total) {
     pdl_wait();   // everything in front is complete before anything is read; then the next kernel may be set up meanwhile
     pdl_launch_dependents();
-    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * V;
     if (i >= total) return;
     const float ap = softplus_e(pq[0]), an = 0.5f + softplus_e(pq[1]);
-    const float z = to_float(x[i]);
-    const float v = z > 0.f ? fmaf(ap * z, z, 0.5f * z) : fmaf(an, expm1f(z) - z, 0.5f * z);
-    out[i] = from_float<T>(v);
+    Pack<T, V> pk = load_pack<T, V>(x + i);
+#pragma unroll
+    for (int k = 0; k < V; k++) {
+        const float z = to_float(pk.v[k]);
+        pk.v[k] = from_float<T>(z > 0.f ? fmaf(ap * z, z, 0.5f * z) : fmaf(an, expm1f(z) - z, 0.5f * z));
+    }
+    store_pack<T, V>(out + i, pk);
 }
 
 // x[t, h, v] <- x[t, h, v] * sigmoid(g[t, per_head ? h : h * vdim + v])
-template <typename T>
+template <typename T, int V>
 __global__ void sigmoid_gate_kernel(T* __restrict__ x, const T* __restrict__ g, int heads, int vdim, long ldg, int per_head,
                                     size_t total) {
     pdl_wait();   // everything in front is complete before anything is read; then the next kernel may be set up meanwhile
     pdl_launch_dependents();
-    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * V;   // V neighbours of one head (vdim is a multiple of V)
     if (i >= total) return;
     const int width = heads * vdim;
     const size_t t = i / width;
     const int c = (int)(i - t * width);
-    const float gate = to_float(g[t * ldg + (per_head ? c / vdim : c)]);
-    x[i] = from_float<T>(to_float(x[i]) / (1.0f + expf(-gate)));
+    Pack<T, V> pk = load_pack<T, V>(x + i);
+    if (per_head) {
+        const float s = 1.0f / (1.0f + expf(-to_float(g[t * ldg + c / vdim])));
+#pragma unroll
+        for (int k = 0; k < V; k++) pk.v[k] = from_float<T>(to_float(pk.v[k]) * s);
+    } else {
+#pragma unroll
+        for (int k = 0; k < V; k++) pk.v[k] = from_float<T>(to_float(pk.v[k]) / (1.0f + expf(-to_float(g[t * ldg + c + k]))));
+    }
+    store_pack<T, V>(x + i, pk);
 }
 
 // x <- cap * tanh(x / cap)
@@ -71,14 +110,26 @@ HYMT2_API int hymt2_bias_act(void* x, int dtype, const float* bias, int rows, in
     if (rows == 0 || cols == 0) return HYMT2_OK;
     HYMT2_REQUIRE(rows > 0 && cols > 0 && ld >= cols && act_cols >= 0 && act_cols <= cols, "bias_act: bad sizes");
     const size_t total = (size_t)rows * cols;
-    HYMT2_DISPATCH_DTYPE(dtype, T, launch_pdl(bias_act_kernel<T>, dim3(blocks_for(total)), dim3(256), 0, stream, (T*)x, bias, cols, ld, act_cols, total));
+    HYMT2_DISPATCH_DTYPE(dtype, T, {
+        constexpr int V = 16 / sizeof(T);
+        if (cols % V == 0 && ld % V == 0 && (uintptr_t)x % 16 == 0)
+            launch_pdl(bias_act_kernel<T, V>, dim3(blocks_for(total / V)), dim3(256), 0, stream, (T*)x, bias, cols, ld, act_cols, total);
+        else
+            launch_pdl(bias_act_kernel<T, 1>, dim3(blocks_for(total)), dim3(256), 0, stream, (T*)x, bias, cols, ld, act_cols, total);
+    });
     return hymt2_check_launch("bias_act");
 }
 
 HYMT2_API int hymt2_xielu(void* out, const void* x, int dtype, const float* pq, long total, cudaStream_t stream) {
     if (total == 0) return HYMT2_OK;
     HYMT2_REQUIRE(total > 0 && pq != nullptr, "xielu: bad sizes");
-    HYMT2_DISPATCH_DTYPE(dtype, T, launch_pdl(xielu_kernel<T>, dim3(blocks_for((size_t)total)), dim3(256), 0, stream, (T*)out, (const T*)x, pq, (size_t)total));
+    HYMT2_DISPATCH_DTYPE(dtype, T, {
+        constexpr int V = 16 / sizeof(T);
+        if (total % V == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)out % 16 == 0)
+            launch_pdl(xielu_kernel<T, V>, dim3(blocks_for((size_t)total / V)), dim3(256), 0, stream, (T*)out, (const T*)x, pq, (size_t)total);
+        else
+            launch_pdl(xielu_kernel<T, 1>, dim3(blocks_for((size_t)total)), dim3(256), 0, stream, (T*)out, (const T*)x, pq, (size_t)total);
+    });
     return hymt2_check_launch("xielu");
 }
 
@@ -87,7 +138,13 @@ HYMT2_API int hymt2_sigmoid_gate(void* x, const void* g, int dtype, int rows, in
     if (rows == 0) return HYMT2_OK;
     HYMT2_REQUIRE(rows > 0 && heads > 0 && vdim > 0, "sigmoid_gate: bad sizes");
     const size_t total = (size_t)rows * heads * vdim;
-    HYMT2_DISPATCH_DTYPE(dtype, T, launch_pdl(sigmoid_gate_kernel<T>, dim3(blocks_for(total)), dim3(256), 0, stream, (T*)x, (const T*)g, heads, vdim, ldg, per_head, total));
+    HYMT2_DISPATCH_DTYPE(dtype, T, {
+        constexpr int V = 16 / sizeof(T);
+        if (vdim % V == 0 && (uintptr_t)x % 16 == 0)
+            launch_pdl(sigmoid_gate_kernel<T, V>, dim3(blocks_for(total / V)), dim3(256), 0, stream, (T*)x, (const T*)g, heads, vdim, ldg, per_head, total);
+        else
+            launch_pdl(sigmoid_gate_kernel<T, 1>, dim3(blocks_for(total)), dim3(256), 0, stream, (T*)x, (const T*)g, heads, vdim, ldg, per_head, total);
+    });
     return hymt2_check_launch("sigmoid_gate");
 }
 

@@ -19,7 +19,8 @@ namespace {
 
 struct LatentPrepParams {
     const void* proj;     // [T, ldp]
-    void* q_out;          // [T, heads * (rank + rot)]
+    void* q_out;          // [T, heads * (rank + rot)], or null: the rotated query parts go back into proj, in place
+    void* rows_out;       // [T, rank + rot] or null: the compressed rows once more, side by side for all tokens
     void* cache;          // plane base, or null: nothing is written (a run that reads another run's cache)
     const int* block_table;
     const int* token_seq;
@@ -62,26 +63,37 @@ latent_prep_kernel(LatentPrepParams p) {
     }
     ss = block_sum(ss, scratch);
     const int dl = p.rank + p.rot;
+    T* dst = nullptr;    // the token's cache row
     if (p.cache && slot >= 0) {
         const int block = p.block_table[(size_t)slot * p.table_stride + pos / p.block_tokens];
-        T* dst = (T*)p.cache + ((size_t)block * p.block_tokens + (pos % p.block_tokens)) * dl;
+        dst = (T*)p.cache + ((size_t)block * p.block_tokens + (pos % p.block_tokens)) * dl;
+    }
+    T* dst2 = p.rows_out ? (T*)p.rows_out + (size_t)t * dl : nullptr;
+    if (dst || dst2) {
         const float scale = 1.0f / sqrtf(ss / (float)p.rank + p.eps);
-        for (int i = threadIdx.x; i < p.rank; i += blockDim.x) dst[i] = from_float<T>(to_float(lat[i]) * scale * p.gain[i]);
+        for (int i = threadIdx.x; i < p.rank; i += blockDim.x) {
+            const T v = from_float<T>(to_float(lat[i]) * scale * p.gain[i]);
+            if (dst) dst[i] = v;
+            if (dst2) dst2[i] = v;
+        }
         const T* kr = lat + p.rank;
         for (int i = threadIdx.x; i < half; i += blockDim.x) {
             const float a = to_float(kr[2 * i]), b = to_float(kr[2 * i + 1]);
-            dst[p.rank + 2 * i] = from_float<T>(a * cs[2 * i] - b * cs[2 * i + 1]);
-            dst[p.rank + 2 * i + 1] = from_float<T>(b * cs[2 * i] + a * cs[2 * i + 1]);
+            const T v0 = from_float<T>(a * cs[2 * i] - b * cs[2 * i + 1]), v1 = from_float<T>(b * cs[2 * i] + a * cs[2 * i + 1]);
+            if (dst) { dst[p.rank + 2 * i] = v0; dst[p.rank + 2 * i + 1] = v1; }
+            if (dst2) { dst2[p.rank + 2 * i] = v0; dst2[p.rank + 2 * i + 1] = v1; }
         }
-        for (int i = p.rot_dims + threadIdx.x; i < p.rot; i += blockDim.x) dst[p.rank + i] = kr[i];
+        for (int i = p.rot_dims + threadIdx.x; i < p.rot; i += blockDim.x) {
+            if (dst) dst[p.rank + i] = kr[i];
+            if (dst2) dst2[p.rank + i] = kr[i];
+        }
     }
     // the heads' rotated query parts
-    T* qo = (T*)p.q_out + (size_t)t * p.heads * dl;
     const int per_head = half + (p.rot - p.rot_dims);
     for (int item = threadIdx.x; item < p.heads * per_head; item += blockDim.x) {
         const int h = item / per_head, i = item - h * per_head;
         const T* q = row + (size_t)h * (p.dim + p.rot) + p.dim;
-        T* o = qo + (size_t)h * dl + p.rank;
+        T* o = p.q_out ? (T*)p.q_out + (size_t)t * p.heads * dl + (size_t)h * dl + p.rank : const_cast<T*>(q);
         if (i < half) {
             const float a = to_float(q[2 * i]), b = to_float(q[2 * i + 1]);
             o[2 * i] = from_float<T>(a * cs[2 * i] - b * cs[2 * i + 1]);
@@ -95,7 +107,7 @@ latent_prep_kernel(LatentPrepParams p) {
 
 }  // namespace
 
-HYMT2_API int hymt2_latent_prep(const void* proj, long ldp, int q_cols, void* q_out, void* cache, int dtype,
+HYMT2_API int hymt2_latent_prep(const void* proj, long ldp, int q_cols, void* q_out, void* rows_out, void* cache, int dtype,
                                 const int* block_table, int table_stride, int block_tokens, const int* token_seq,
                                 const int* token_pos, const int* slot_ids, const float* gain, const float* inv_freq,
                                 int rot_dims, float amplitude, float eps, int tokens, int heads, int dim, int rot, int rank,
@@ -105,7 +117,7 @@ HYMT2_API int hymt2_latent_prep(const void* proj, long ldp, int q_cols, void* q_
     HYMT2_REQUIRE(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= rot, "latent_prep: %d rotated entries of %d", rot_dims, rot);
     HYMT2_REQUIRE(rot_dims == 0 || inv_freq != nullptr, "latent_prep: no frequencies");
     LatentPrepParams p;
-    p.proj = proj; p.q_out = q_out; p.cache = cache; p.block_table = block_table; p.token_seq = token_seq;
+    p.proj = proj; p.q_out = q_out; p.rows_out = rows_out; p.cache = cache; p.block_table = block_table; p.token_seq = token_seq;
     p.token_pos = token_pos; p.slot_ids = slot_ids; p.gain = gain; p.inv_freq = inv_freq; p.ldp = ldp; p.q_cols = q_cols;
     p.table_stride = table_stride; p.block_tokens = block_tokens; p.heads = heads; p.dim = dim; p.rot = rot; p.rank = rank;
     p.rot_dims = rot_dims; p.eps = eps; p.amplitude = amplitude;

@@ -11,6 +11,13 @@
 // Row r of sequence b (token r / heads of its new tokens) sits at position p = kv_len - n_b + r / heads and sees the
 // keys max(0, p - window + 1) .. p.  With split_keys > 0 (decode steps) a block takes one chunk of that many keys
 // and leaves unnormalised partials, which the merge kernel of the CUDA-core attention folds in chunk order.
+//
+// The same kernel has a second form (EXPANDED) for prompts that start at position 0, where every key of a sequence is
+// one of the step's own tokens: keys and values are then worth rebuilding per head (K_h = [W_uk[h] c | rotated part],
+// V_h = W_uv[h] c, made by one product for all tokens) because a head's rows are several times narrower than the
+// compressed row.  A block then owns 64 TOKENS of ONE head; queries, keys and values are read from the matrices that
+// the projections left, the key tile is put together from the head's own columns and the shared rotated part, and the
+// values have a tile of their own.
 #include "common.cuh"
 
 #include <mma.h>
@@ -38,10 +45,16 @@ struct LatentMmaParams {
     float* part_ml;       // [T * nh, splits, 2]
     int table_stride, nh, d, dv, window, split_keys, max_splits;
     float scale;
+    // the expanded form: q is the projection [T, ldq_g] with head h's d entries at column h * d; out is [T, ld_out]
+    const bf16* kexp;     // [T, ld_kexp]: head h's unrotated key entries at column h * dim
+    const bf16* vexp;     // [T, ld_vexp]: head h's values at column h * dv
+    const bf16* krot;     // [T, ld_krot]: the rotated key part that all heads share
+    long ldq_g, ld_out, ld_kexp, ld_vexp, ld_krot;
+    int dim;              // unrotated entries of a key (d - dim are the rotated ones)
 };
 
-template <int MAXF>
-__global__ void __launch_bounds__(THREADS, 1)
+template <int MAXF, bool EXPANDED>
+__global__ void __launch_bounds__(THREADS, EXPANDED ? 2 : 1)
 latent_attention_mma_kernel(LatentMmaParams p) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int d = p.d, dv = p.dv, ldq = d + 8;
@@ -52,16 +65,19 @@ latent_attention_mma_kernel(LatentMmaParams p) {
     float* m_s = reinterpret_cast<float*>(Ps + MT * P_LD);  // [64] running maximum
     float* l_s = m_s + MT;                                  // [64] running sum
     float* corr_s = l_s + MT;                               // [64] what the old sums shrink by in this tile
+    bf16* Vs = reinterpret_cast<bf16*>(corr_s + MT);        // [64][dv + 8], the expanded form only
+    const int ldv = EXPANDED ? dv + 8 : ldq;
+    const int head = EXPANDED ? blockIdx.y : 0;
 
     const int b = blockIdx.z / p.max_splits, split = blockIdx.z % p.max_splits;
     const int slot = p.slot_ids[b];
     if (slot < 0) return;
     const int tok0 = p.cu_seqlens[b], n = p.cu_seqlens[b + 1] - tok0;
     const int kv_len = p.kv_lens[b], start = kv_len - n;
-    const int rows_total = n * p.nh, r0 = blockIdx.x * MT;
+    const int rows_total = EXPANDED ? n : n * p.nh, r0 = blockIdx.x * MT;
     if (r0 >= rows_total) return;
     const int rows_valid = min(MT, rows_total - r0);
-    const int first_tok = r0 / p.nh, last_tok = (r0 + rows_valid - 1) / p.nh;
+    const int first_tok = EXPANDED ? r0 : r0 / p.nh, last_tok = EXPANDED ? r0 + rows_valid - 1 : (r0 + rows_valid - 1) / p.nh;
     int key_end = start + last_tok + 1;
     int key_begin = p.window > 0 ? max(0, start + first_tok - p.window + 1) : 0;
     if (p.split_keys > 0) {
@@ -74,11 +90,12 @@ latent_attention_mma_kernel(LatentMmaParams p) {
     const size_t row_base = (size_t)tok0 * p.nh + r0;     // first of this tile's rows among all (token, head) rows
 
     // the queries
-    const bf16* qg = p.q + row_base * d;
+    const bf16* qg = EXPANDED ? p.q + (size_t)(tok0 + r0) * p.ldq_g + (size_t)head * d : p.q + row_base * d;
+    const size_t q_ld = EXPANDED ? (size_t)p.ldq_g : (size_t)d;
     for (int i = tid * 8; i < MT * d; i += THREADS * 8) {
         const int r = i / d, c = i - r * d;
         uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (r < rows_valid) v = *reinterpret_cast<const uint4*>(qg + (size_t)r * d + c);
+        if (r < rows_valid) v = *reinterpret_cast<const uint4*>(qg + (size_t)r * q_ld + c);
         *reinterpret_cast<uint4*>(Qs + r * ldq + c) = v;
     }
     if (tid < MT) { m_s[tid] = -INFINITY; l_s[tid] = 0.f; corr_s[tid] = 1.f; }
@@ -106,14 +123,33 @@ latent_attention_mma_kernel(LatentMmaParams p) {
     const int* table = p.block_table + (size_t)slot * p.table_stride;
     for (int k0 = (key_begin / NT) * NT; k0 < key_end; k0 += NT) {
         __syncthreads();   // the tile before is done with Ks and Ps (and, first time round, Qs and the statistics are written)
-        const int block = table[k0 / NT];
-        const bf16* kg = p.cache + (size_t)(block < 0 ? 0 : block) * NT * d;
-        const int keys_here = block < 0 ? 0 : min(NT, kv_len - k0);   // rows past the sequence's end hold anything: they are zeroed
-        for (int i = tid * 8; i < NT * d; i += THREADS * 8) {
-            const int r = i / d, c = i - r * d;
-            uint4 v = make_uint4(0u, 0u, 0u, 0u);
-            if (r < keys_here) v = *reinterpret_cast<const uint4*>(kg + i);
-            *reinterpret_cast<uint4*>(Ks + r * ldq + c) = v;
+        if (EXPANDED) {
+            const int keys_here = min(NT, n - k0);   // (the sequence starts in this step: its keys are its new tokens)
+            const size_t t0 = (size_t)tok0 + k0;
+            for (int i = tid * 8; i < NT * d; i += THREADS * 8) {
+                const int r = i / d, c = i - r * d;
+                uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                if (r < keys_here)
+                    v = c < p.dim ? *reinterpret_cast<const uint4*>(p.kexp + (t0 + r) * p.ld_kexp + (size_t)head * p.dim + c)
+                                  : *reinterpret_cast<const uint4*>(p.krot + (t0 + r) * p.ld_krot + (c - p.dim));
+                *reinterpret_cast<uint4*>(Ks + r * ldq + c) = v;
+            }
+            for (int i = tid * 8; i < NT * dv; i += THREADS * 8) {
+                const int r = i / dv, c = i - r * dv;
+                uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                if (r < keys_here) v = *reinterpret_cast<const uint4*>(p.vexp + (t0 + r) * p.ld_vexp + (size_t)head * dv + c);
+                *reinterpret_cast<uint4*>(Vs + r * ldv + c) = v;
+            }
+        } else {
+            const int block = table[k0 / NT];
+            const bf16* kg = p.cache + (size_t)(block < 0 ? 0 : block) * NT * d;
+            const int keys_here = block < 0 ? 0 : min(NT, kv_len - k0);   // rows past the sequence's end hold anything: they are zeroed
+            for (int i = tid * 8; i < NT * d; i += THREADS * 8) {
+                const int r = i / d, c = i - r * d;
+                uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                if (r < keys_here) v = *reinterpret_cast<const uint4*>(kg + i);
+                *reinterpret_cast<uint4*>(Ks + r * ldq + c) = v;
+            }
         }
         __syncthreads();
 
@@ -144,7 +180,7 @@ latent_attention_mma_kernel(LatentMmaParams p) {
             const int r = tid >> 2, part = tid & 3;
             const int grow = r0 + r;
             const bool row_ok = r < rows_valid;
-            const int pos = start + grow / p.nh;
+            const int pos = start + (EXPANDED ? grow : grow / p.nh);
             const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
             float s[16];
             float tmax = -INFINITY;
@@ -205,7 +241,7 @@ latent_attention_mma_kernel(LatentMmaParams p) {
                 for (int i = 0; i < MAXF; i++)
                     if (warp + 8 * i < o_frags_total) {
                         wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::row_major> vb;
-                        wmma::load_matrix_sync(vb, Ks + kk * ldq + (cf_o + 2 * i) * 16, ldq);
+                        wmma::load_matrix_sync(vb, (EXPANDED ? Vs : Ks) + kk * ldv + (cf_o + 2 * i) * 16, ldv);
                         wmma::mma_sync(acc[i], a, vb, acc[i]);
                     }
             }
@@ -245,15 +281,17 @@ latent_attention_mma_kernel(LatentMmaParams p) {
                 __nv_bfloat162 h[4];
 #pragma unroll
                 for (int e = 0; e < 4; e++) h[e] = __floats2bfloat162_rn(src[2 * e], src[2 * e + 1]);
-                *reinterpret_cast<uint4*>(p.out + (row_base + row) * dv + col) = *reinterpret_cast<uint4*>(h);
+                bf16* dst = EXPANDED ? p.out + (size_t)(tok0 + r0 + row) * p.ld_out + (size_t)head * dv + col : p.out + (row_base + row) * dv + col;
+                *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<uint4*>(h);
             }
         }
         __syncwarp();
     }
 }
 
-size_t smem_bytes(int d) {
-    return (size_t)2 * MT * (d + 8) * sizeof(bf16) + (size_t)MT * S_LD * sizeof(float) + (size_t)MT * P_LD * sizeof(bf16) + 3 * MT * sizeof(float);
+size_t smem_bytes(int d, int dv_tile = 0) {
+    return (size_t)2 * MT * (d + 8) * sizeof(bf16) + (size_t)MT * S_LD * sizeof(float) + (size_t)MT * P_LD * sizeof(bf16) + 3 * MT * sizeof(float)
+         + (dv_tile ? (size_t)NT * (dv_tile + 8) * sizeof(bf16) : 0);
 }
 
 }  // namespace
@@ -288,11 +326,44 @@ HYMT2_API int hymt2_latent_attention_mma(void* out, const void* q, const void* c
         return hymt2_check_launch("latent_attention_mma");
     };
     int rc;
-    if (dv <= 128) rc = launch(latent_attention_mma_kernel<4>);
-    else if (dv <= 256) rc = launch(latent_attention_mma_kernel<8>);
-    else rc = launch(latent_attention_mma_kernel<16>);
+    if (dv <= 128) rc = launch(latent_attention_mma_kernel<4, false>);
+    else if (dv <= 256) rc = launch(latent_attention_mma_kernel<8, false>);
+    else rc = launch(latent_attention_mma_kernel<16, false>);
     if (rc == HYMT2_OK && split_keys > 0)
         rc = hymt2_attention_merge_launch(out, HYMT2_BF16, cu_seqlens, slot_ids, kv_lens, part_acc, part_ml, tokens, nh, dv, window,
                                           split_keys, max_splits, stream, status);
     return rc;
+}
+
+// The expanded form (see the head of this file): whole prompts from position 0 with per-head keys and values.
+HYMT2_API int hymt2_latent_attention_expanded_supported(int dim, int rot, int dv) {
+    const int d = dim + rot;
+    return dim > 0 && rot >= 0 && dv > 0 && d % 16 == 0 && dv % 16 == 0 && dim % 8 == 0 && dv <= 256 && smem_bytes(d, dv) <= 110 * 1024;
+}
+
+HYMT2_API int hymt2_latent_attention_expanded(void* out, long ld_out, const void* q, long ldq, const void* kexp, long ld_kexp,
+                                              const void* vexp, long ld_vexp, const void* krot, long ld_krot,
+                                              const int* cu_seqlens, const int* slot_ids, const int* kv_lens, int batch,
+                                              int max_new_tokens, int nh, int dim, int rot, int dv, float scale, int window,
+                                              cudaStream_t stream) {
+    if (batch == 0 || max_new_tokens == 0) return HYMT2_OK;
+    HYMT2_REQUIRE(hymt2_latent_attention_expanded_supported(dim, rot, dv), "latent_attention_expanded: heads of %d + %d key entries and %d value entries are not taken", dim, rot, dv);
+    HYMT2_REQUIRE(batch > 0 && batch <= 65535 && nh > 0 && nh <= 65535, "latent_attention_expanded: bad sizes");
+    const uintptr_t bits = (uintptr_t)out | (uintptr_t)q | (uintptr_t)kexp | (uintptr_t)vexp | (uintptr_t)krot;
+    HYMT2_REQUIRE(bits % 16 == 0 && ld_out % 8 == 0 && ldq % 8 == 0 && ld_kexp % 8 == 0 && ld_vexp % 8 == 0 && ld_krot % 8 == 0,
+                  "latent_attention_expanded: operands and rows must be 16-byte aligned");
+    LatentMmaParams p = {};
+    p.q = (const bf16*)q; p.out = (bf16*)out; p.cu_seqlens = cu_seqlens; p.slot_ids = slot_ids; p.kv_lens = kv_lens;
+    p.nh = nh; p.d = dim + rot; p.dv = dv; p.window = window; p.split_keys = 0; p.max_splits = 1; p.scale = scale;
+    p.kexp = (const bf16*)kexp; p.vexp = (const bf16*)vexp; p.krot = (const bf16*)krot;
+    p.ldq_g = ldq; p.ld_out = ld_out; p.ld_kexp = ld_kexp; p.ld_vexp = ld_vexp; p.ld_krot = ld_krot; p.dim = dim;
+    const dim3 grid((max_new_tokens + MT - 1) / MT, nh, batch);
+    const size_t smem = smem_bytes(p.d, dv);
+    auto launch = [&](auto kernel) -> int {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) { hymt2_set_error("latent_attention_expanded: %s", cudaGetErrorString(e)); return HYMT2_ERR_LAUNCH; }
+        kernel<<<grid, THREADS, smem, stream>>>(p);
+        return hymt2_check_launch("latent_attention_expanded");
+    };
+    return dv <= 128 ? launch(latent_attention_mma_kernel<4, true>) : launch(latent_attention_mma_kernel<8, true>);
 }

@@ -105,6 +105,42 @@ __global__ void rmsnorm_groups_kernel(TY* __restrict__ y, const TX* __restrict__
     }
 }
 
+// The same for float32 rows whose parts are whole pieces of four values: 16-byte loads, and 16- or 8-byte stores.
+template <typename TW, typename TY, bool ADD>
+__global__ void rmsnorm_groups_vec_kernel(TY* __restrict__ y, const float* __restrict__ x, const TW* __restrict__ gain,
+                                          const int* __restrict__ rows_index, int dim, int part, float eps, float out_scale) {
+    __shared__ float scratch[33];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int r = blockIdx.x, g = blockIdx.y;
+    const float* src = x + (size_t)(rows_index ? rows_index[r] : r) * dim + (size_t)g * part;
+    float ss = 0.f;
+    for (int i = threadIdx.x * 4; i < part; i += blockDim.x * 4) {
+        const float4 v = *reinterpret_cast<const float4*>(src + i);
+        ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+    }
+    ss = block_sum(ss, scratch);
+    const float scale = out_scale / sqrtf(ss / (float)part + eps);
+    TY* dst = y + (size_t)r * dim + (size_t)g * part;
+    const TW* gn = gain + (size_t)g * part;
+    for (int i = threadIdx.x * 4; i < part; i += blockDim.x * 4) {
+        const float4 v = *reinterpret_cast<const float4*>(src + i);
+        float o[4] = {v.x * scale * to_float(gn[i]), v.y * scale * to_float(gn[i + 1]), v.z * scale * to_float(gn[i + 2]),
+                      v.w * scale * to_float(gn[i + 3])};
+        if constexpr (sizeof(TY) == 4) {
+            float4* d4 = reinterpret_cast<float4*>(dst + i);
+            if constexpr (ADD) {
+                const float4 old = *d4;
+                o[0] += old.x; o[1] += old.y; o[2] += old.z; o[3] += old.w;
+            }
+            *d4 = make_float4(o[0], o[1], o[2], o[3]);
+        } else {
+            __nv_bfloat162 h[2] = {__floats2bfloat162_rn(o[0], o[1]), __floats2bfloat162_rn(o[2], o[3])};
+            *reinterpret_cast<uint2*>(dst + i) = *reinterpret_cast<const uint2*>(h);
+        }
+    }
+}
+
 HYMT2_API int hymt2_rmsnorm_groups(void* y, int y_dtype, const void* x, int x_dtype, const void* gain, int gain_dtype,
                                    const int* rows_index, int rows, int dim, int groups, float eps, float out_scale,
                                    int add, cudaStream_t stream) {
@@ -115,6 +151,18 @@ HYMT2_API int hymt2_rmsnorm_groups(void* y, int y_dtype, const void* x, int x_dt
     const int part = dim / groups;
     const int threads = part >= 1024 ? 256 : (part >= 256 ? 128 : (part >= 64 ? 64 : 32));
     const dim3 grid(rows, groups);
+    if (x_dtype == HYMT2_F32 && part % 4 == 0 && dim % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)y % 16 == 0) {
+        const int vt = part >= 1024 ? 256 : (part >= 512 ? 128 : (part >= 256 ? 64 : 32));
+        HYMT2_DISPATCH_DTYPE(gain_dtype, TW, {
+            if (add)
+                launch_pdl(rmsnorm_groups_vec_kernel<TW, float, true>, grid, dim3(vt), 0, stream, (float*)y, (const float*)x, (const TW*)gain,
+                           rows_index, dim, part, eps, out_scale);
+            else
+                HYMT2_DISPATCH_DTYPE(y_dtype, TY, (launch_pdl(rmsnorm_groups_vec_kernel<TW, TY, false>, grid, dim3(vt), 0, stream, (TY*)y,
+                                                              (const float*)x, (const TW*)gain, rows_index, dim, part, eps, out_scale)));
+        });
+        return hymt2_check_launch("rmsnorm_groups");
+    }
     HYMT2_DISPATCH_DTYPE(x_dtype, TX, HYMT2_DISPATCH_DTYPE(gain_dtype, TW, {
         if (add) {
             launch_pdl(rmsnorm_groups_kernel<TX, TW, float, true>, grid, dim3(threads), 0, stream, (float*)y, (const TX*)x, (const TW*)gain,

@@ -26,12 +26,31 @@ struct ConvParams {
 // One thread owns a channel over a chunk of a sequence's new tokens and slides a window of registers over it.  The
 // thread of the first chunk is the only one that reads the state (for the inputs before this step) and, once it has,
 // writes the new one: the last taps - 1 inputs of (old state, new tokens).
-template <typename T>
+template <typename T, int V> struct ChanPack { T v[V]; };
+template <typename T, int V> __device__ __forceinline__ void load_chan(const T* p, float out[V]) {
+    ChanPack<T, V> r;
+    if constexpr (V == 1) r.v[0] = *p;
+    else if constexpr (V * sizeof(T) == 4) *reinterpret_cast<uint32_t*>(r.v) = *reinterpret_cast<const uint32_t*>(p);
+    else *reinterpret_cast<uint2*>(r.v) = *reinterpret_cast<const uint2*>(p);
+#pragma unroll
+    for (int k = 0; k < V; k++) out[k] = to_float(r.v[k]);
+}
+template <typename T, int V> __device__ __forceinline__ void store_chan(T* p, const float in[V]) {
+    ChanPack<T, V> r;
+#pragma unroll
+    for (int k = 0; k < V; k++) r.v[k] = from_float<T>(in[k]);
+    if constexpr (V == 1) *p = r.v[0];
+    else if constexpr (V * sizeof(T) == 4) *reinterpret_cast<uint32_t*>(p) = *reinterpret_cast<const uint32_t*>(r.v);
+    else *reinterpret_cast<uint2*>(p) = *reinterpret_cast<const uint2*>(r.v);
+}
+
+// A thread owns V neighbouring channels (V = 2 where the rows allow 4- or 8-byte accesses).
+template <typename T, int V>
 __global__ void __launch_bounds__(CONV_THREADS)
 causal_conv_kernel(ConvParams p) {
     pdl_wait();   // everything in front is complete before anything is read; then the next kernel may be set up meanwhile
     pdl_launch_dependents();
-    const int c = blockIdx.x * CONV_THREADS + threadIdx.x;
+    const int c = (blockIdx.x * CONV_THREADS + threadIdx.x) * V;
     const int b = blockIdx.z;
     if (c >= p.channels) return;
     const int tok0 = p.cu_seqlens[b], n = p.cu_seqlens[b + 1] - tok0;
@@ -41,53 +60,82 @@ causal_conv_kernel(ConvParams p) {
     const T* x = (const T*)p.x + (size_t)tok0 * p.ldx + c;
     T* out = (T*)p.out + (size_t)tok0 * p.ldo + c;
     const int i1 = min(n, i0 + CONV_CHUNK);
+    float zero[V];
+#pragma unroll
+    for (int k = 0; k < V; k++) zero[k] = 0.f;
     if (slot < 0) {   // a padding row: nothing is remembered, the output is defined
-        for (int i = i0; i < i1; i++) out[(size_t)i * p.ldo] = from_float<T>(0.f);
+        for (int i = i0; i < i1; i++) store_chan<T, V>(out + (size_t)i * p.ldo, zero);
         return;
     }
     const int start = p.kv_lens[b] - n;   // position of the step's first token
     const int taps = p.taps, hist = taps - 1;
     float* st = (float*)(p.state + (size_t)slot * p.state_stride) + c;   // st[j * channels], j = 0 oldest
-    float w[CONV_MAX_TAPS], win[CONV_MAX_TAPS];
+    float w[CONV_MAX_TAPS][V], win[CONV_MAX_TAPS][V];
 #pragma unroll
-    for (int j = 0; j < CONV_MAX_TAPS; j++) w[j] = j < taps ? p.w[(size_t)c * taps + j] : 0.f;
+    for (int j = 0; j < CONV_MAX_TAPS; j++)
+#pragma unroll
+        for (int k = 0; k < V; k++) w[j][k] = j < taps ? p.w[(size_t)(c + k) * taps + j] : 0.f;
     // win[j] for j < hist: the input at index i0 - hist + j among the new tokens
 #pragma unroll
     for (int j = 0; j < CONV_MAX_TAPS; j++) {
-        win[j] = 0.f;
+#pragma unroll
+        for (int k = 0; k < V; k++) win[j][k] = 0.f;
         if (j < hist) {
             const int idx = i0 - hist + j;
-            if (idx >= 0) win[j] = to_float(x[(size_t)idx * p.ldx]);
-            else if (start + idx >= 0) win[j] = st[(size_t)(hist + idx) * p.channels];
+            if (idx >= 0) load_chan<T, V>(x + (size_t)idx * p.ldx, win[j]);
+            else if (start + idx >= 0) {
+#pragma unroll
+                for (int k = 0; k < V; k++) win[j][k] = st[(size_t)(hist + idx) * p.channels + k];
+            }
         }
     }
-    const float bias = p.bias ? p.bias[c] : 0.f;
+    float bias[V];
+#pragma unroll
+    for (int k = 0; k < V; k++) bias[k] = p.bias ? p.bias[c + k] : 0.f;
     for (int i = i0; i < i1; i++) {
-        const float cur = to_float(x[(size_t)i * p.ldx]);
-        float acc = 0.f;
+        float cur[V], acc[V];
+        load_chan<T, V>(x + (size_t)i * p.ldx, cur);
 #pragma unroll
-        for (int j = 0; j < CONV_MAX_TAPS; j++)
-            if (j < hist) acc = fmaf(w[j], win[j], acc);
-        acc = fmaf(w[hist], cur, acc) + bias;
-        if (p.add_input) acc += cur;
-        out[(size_t)i * p.ldo] = from_float<T>(acc);
-#pragma unroll
-        for (int j = 0; j < CONV_MAX_TAPS - 1; j++)
-            if (j + 1 < hist) win[j] = win[j + 1];
-        if (hist > 0) {
+        for (int k = 0; k < V; k++) {
+            float a = 0.f;
 #pragma unroll
             for (int j = 0; j < CONV_MAX_TAPS; j++)
-                if (j == hist - 1) win[j] = cur;
+                if (j < hist) a = fmaf(w[j][k], win[j][k], a);
+#pragma unroll
+            for (int j = 0; j < CONV_MAX_TAPS; j++)
+                if (j == hist) a = fmaf(w[j][k], cur[k], a);
+            a += bias[k];
+            if (p.add_input) a += cur[k];
+            acc[k] = a;
         }
+        store_chan<T, V>(out + (size_t)i * p.ldo, acc);
+#pragma unroll
+        for (int j = 0; j < CONV_MAX_TAPS - 1; j++)
+            if (j + 1 < hist) {
+#pragma unroll
+                for (int k = 0; k < V; k++) win[j][k] = win[j + 1][k];
+            }
+#pragma unroll
+        for (int j = 0; j < CONV_MAX_TAPS; j++)
+            if (j == hist - 1) {
+#pragma unroll
+                for (int k = 0; k < V; k++) win[j][k] = cur[k];
+            }
     }
     if (i0 == 0) {
         // new[j] = combined[n + j] of combined = (old state, new tokens); ascending j reads only what is not yet overwritten
         for (int j = 0; j < hist; j++) {
             const int idx = n - hist + j;   // among the new tokens
-            float v = 0.f;
-            if (idx >= 0) v = to_float(x[(size_t)idx * p.ldx]);
-            else if (start + idx >= 0) v = st[(size_t)(hist + idx) * p.channels];
-            st[(size_t)j * p.channels] = v;
+            float v[V];
+#pragma unroll
+            for (int k = 0; k < V; k++) v[k] = 0.f;
+            if (idx >= 0) load_chan<T, V>(x + (size_t)idx * p.ldx, v);
+            else if (start + idx >= 0) {
+#pragma unroll
+                for (int k = 0; k < V; k++) v[k] = st[(size_t)(hist + idx) * p.channels + k];
+            }
+#pragma unroll
+            for (int k = 0; k < V; k++) st[(size_t)j * p.channels + k] = v[k];
         }
     }
 }
@@ -242,8 +290,16 @@ HYMT2_API int hymt2_causal_conv(void* out, const void* x, int dtype, const float
     p.channels = channels; p.taps = taps; p.ldx = ldx; p.ldo = ldo; p.add_input = add_input;
     const int chunks = (max_new_tokens + CONV_CHUNK - 1) / CONV_CHUNK;
     HYMT2_REQUIRE(chunks <= 65535, "causal_conv: %d tokens in one sequence are too many for one launch", max_new_tokens);
-    const dim3 grid((channels + CONV_THREADS - 1) / CONV_THREADS, chunks, batch);
-    HYMT2_DISPATCH_DTYPE(dtype, T, launch_pdl(causal_conv_kernel<T>, grid, dim3(CONV_THREADS), 0, stream, p));
+    HYMT2_DISPATCH_DTYPE(dtype, T, {
+        const bool pairs = channels % 2 == 0 && ldx % 2 == 0 && ldo % 2 == 0 && (uintptr_t)x % (2 * sizeof(T)) == 0 && (uintptr_t)out % (2 * sizeof(T)) == 0;
+        if (pairs) {
+            const dim3 grid((channels / 2 + CONV_THREADS - 1) / CONV_THREADS, chunks, batch);
+            launch_pdl(causal_conv_kernel<T, 2>, grid, dim3(CONV_THREADS), 0, stream, p);
+        } else {
+            const dim3 grid((channels + CONV_THREADS - 1) / CONV_THREADS, chunks, batch);
+            launch_pdl(causal_conv_kernel<T, 1>, grid, dim3(CONV_THREADS), 0, stream, p);
+        }
+    });
     return hymt2_check_launch("causal_conv");
 }
 

@@ -935,20 +935,25 @@ def gemm_simt_batched(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, batch
                                           _stream()), "gemm_simt_batched")
 
 
-def latent_prep(proj: torch.Tensor, q_cols: int, q_out: torch.Tensor, cache_plane: torch.Tensor | None, block_table: torch.Tensor,
+def latent_prep(proj: torch.Tensor, q_cols: int, q_out: torch.Tensor | None, cache_plane: torch.Tensor | None, block_table: torch.Tensor,
                 block_tokens: int, token_seq: torch.Tensor, token_pos: torch.Tensor, slot_ids: torch.Tensor, gain: torch.Tensor,
                 inv_freq: torch.Tensor | None, rot_dims: int, amplitude: float, eps: float, heads: int, dim: int, rot: int,
-                rank: int) -> None:
+                rank: int, rows_out: torch.Tensor | None = None) -> None:
     """From a token's fused projection [heads * (dim + rot) query entries | rank latent entries | rot shared key entries]:
     the normed latent vector and the rotated shared key part go to the token's cache row [rank + rot]; every head's
     rotated query part goes to q_out[t, h, rank : rank + rot].  Pairs (2i, 2i+1) turn by position * inv_freq[i], cosine
-    and sine times `amplitude`.  cache_plane None: nothing is cached."""
+    and sine times `amplitude`.  cache_plane None: nothing is cached.  q_out None: the rotated query parts are written
+    back into proj, in place.  rows_out [T, rank + rot]: the cache rows once more, side by side for all tokens."""
     ldp = _rows_view(proj, "proj")
     T = proj.shape[0]
     dl = rank + rot
-    _need(q_out, "q_out", proj.dtype, 2)
-    if proj.shape[1] < q_cols + dl or q_cols != heads * (dim + rot) or q_out.shape != (T, heads * dl):
-        raise KernelError(f"latent_prep: shapes proj {tuple(proj.shape)} q_out {tuple(q_out.shape)}")
+    if q_out is not None:
+        _need(q_out, "q_out", proj.dtype, 2)
+    if rows_out is not None:
+        _need(rows_out, "rows_out", proj.dtype, 2)
+    if proj.shape[1] < q_cols + dl or q_cols != heads * (dim + rot) or (q_out is not None and q_out.shape != (T, heads * dl)) \
+            or (rows_out is not None and rows_out.shape != (T, dl)):
+        raise KernelError(f"latent_prep: shapes proj {tuple(proj.shape)} do not fit {heads} heads of {dim} + {rot} and a row of {dl}")
     if cache_plane is not None:
         _need(cache_plane, "cache_plane", proj.dtype, 4)
         if cache_plane.shape[1:] != (1, block_tokens, dl):
@@ -957,7 +962,7 @@ def latent_prep(proj: torch.Tensor, q_cols: int, q_out: torch.Tensor, cache_plan
     for t, n in ((token_seq, "token_seq"), (token_pos, "token_pos"), (slot_ids, "slot_ids")):
         _need(t, n, torch.int32, 1)
     _f32(gain, "gain", rank); _f32(inv_freq, "inv_freq", rot_dims // 2)
-    _check(_lib().hymt2_latent_prep(_ptr(proj), c_long(ldp), c_int(q_cols), _ptr(q_out), _ptr(cache_plane), c_int(dtype_code(proj.dtype)),
+    _check(_lib().hymt2_latent_prep(_ptr(proj), c_long(ldp), c_int(q_cols), _ptr(q_out), _ptr(rows_out), _ptr(cache_plane), c_int(dtype_code(proj.dtype)),
                                     _ptr(block_table), c_int(block_table.stride(0)), c_int(block_tokens), _ptr(token_seq),
                                     _ptr(token_pos), _ptr(slot_ids), _ptr(gain), _ptr(inv_freq), c_int(rot_dims), c_float(amplitude),
                                     c_float(eps), c_int(T), c_int(heads), c_int(dim), c_int(rot), c_int(rank), _stream()), "latent_prep")
@@ -1047,3 +1052,37 @@ def gemm_skinny_batched(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, a_s
     _check(_lib().hymt2_gemm_skinny_batched(_ptr(out), c_int(dtype_code(out.dtype)), _ptr(a), _ptr(w), c_int(dtype_code(a.dtype)),
                                             c_int(a.shape[0]), c_int(N), c_int(K), c_long(lda), c_long(ldc), c_int(batch),
                                             c_long(a_step), c_long(N * K), c_long(out_step), _stream()), "gemm_skinny_batched")
+
+
+def latent_attention_expanded_supported(dtype: torch.dtype, dim: int, rot: int, dv: int) -> bool:
+    """Whether the per-head form of the tensor-core latent attention takes these head sizes."""
+    if dtype != torch.bfloat16:
+        return False
+    key = ("expanded", dim, rot, dv)
+    hit = _mma_ok.get(key)
+    if hit is None:
+        hit = _mma_ok[key] = bool(_lib().hymt2_latent_attention_expanded_supported(c_int(dim), c_int(rot), c_int(dv)))
+    return hit
+
+
+def latent_attention_expanded(out: torch.Tensor, q: torch.Tensor, kexp: torch.Tensor, vexp: torch.Tensor, krot: torch.Tensor,
+                              cu_seqlens: torch.Tensor, slot_ids: torch.Tensor, kv_lens: torch.Tensor, batch: int,
+                              max_new_tokens: int, nh: int, dim: int, rot: int, dv: int, scale: float, window: int = 0) -> None:
+    """Causal attention of whole prompts that start at position 0, bfloat16 on the tensor cores, with keys and values per
+    head: q [T, >= nh * (dim + rot)] (head h at column h * (dim + rot), its last rot entries rotated), kexp [T, nh * dim],
+    vexp [T, nh * dv], krot [T, rot] the rotated key part of all heads; out [T, nh * dv].  All may be columns of wider
+    matrices."""
+    T = out.shape[0]
+    for t, n in ((out, "out"), (q, "q"), (kexp, "kexp"), (vexp, "vexp"), (krot, "krot")):
+        _rows_view(t, n, torch.bfloat16)
+        if t.shape[0] != T:
+            raise KernelError(f"latent_attention_expanded: {n} has {t.shape[0]} rows, expected {T}")
+    if out.shape[1] != nh * dv or q.shape[1] < nh * (dim + rot) or kexp.shape[1] != nh * dim or vexp.shape[1] != nh * dv or krot.shape[1] != rot:
+        raise KernelError("latent_attention_expanded: the matrices do not fit the head sizes")
+    for t, n in ((cu_seqlens, "cu_seqlens"), (slot_ids, "slot_ids"), (kv_lens, "kv_lens")):
+        _need(t, n, torch.int32, 1)
+    _check(_lib().hymt2_latent_attention_expanded(_ptr(out), c_long(out.stride(0)), _ptr(q), c_long(q.stride(0)), _ptr(kexp),
+                                                  c_long(kexp.stride(0)), _ptr(vexp), c_long(vexp.stride(0)), _ptr(krot),
+                                                  c_long(krot.stride(0)), _ptr(cu_seqlens), _ptr(slot_ids), _ptr(kv_lens), c_int(batch),
+                                                  c_int(max_new_tokens), c_int(nh), c_int(dim), c_int(rot), c_int(dv), c_float(scale),
+                                                  c_int(window), _stream()), "latent_attention_expanded")

@@ -11,6 +11,10 @@ so the attention runs in the compressed space, with a query of kv_rank + rot_dim
 row, whose first kv_rank entries are also the value.  Then an output gate (sigmoid of a projection of the mixer's
 input, one value per output entry or one per head) and the output projection.  Scores, softmax, the latent norm and
 the rotation are float32; the projections run in the engine's compute type.
+
+A prompt that starts at position 0 brings all of its keys along, and a head's own rows (dim + rot_dim, vdim) are several
+times narrower than the compressed row: there the bfloat16 engine rebuilds every head's keys and values with one product
+over all tokens and runs the attention per head, which is the same sums in another order (EXPAND_FROM_TOKENS).
 """
 from __future__ import annotations
 
@@ -22,6 +26,7 @@ from ..weights.loader import TensorSpec
 from .base import MixerSlot, PartSpec, build_part, register_part
 from .linear import Linear, compute_form, matmul_batched
 
+EXPAND_FROM_TOKENS = 32   # prompts from this length on are worth one more product (keys and values per head)
 SPLIT_KEYS = 256     # decode: keys per partial, a constant so that the cut depends on nothing else
 SPLIT_KEYS_TC = 128  # the same for the tensor-core kernel, whose blocks are few and large: more of them per sequence
 
@@ -42,7 +47,7 @@ class LatentAttention:
         self.position = build_part("position", position) if position is not None else None
         self.q_cols = heads * (dim + rot_dim)
         self.gate_cols = 0 if gate is None else (heads * vdim if gate == "element" else heads)
-        self.proj = self.out = self.uk_t = self.uv = self.c_gain = None
+        self.proj = self.out = self.uk_t = self.uv = self.c_gain = self.ukv = None
 
     # -- what it needs ----------------------------------------------------------
     def tensors(self):
@@ -66,6 +71,10 @@ class LatentAttention:
     def load(self, weights, device, dtype):
         n, H = self.names, self.heads
         rows = [weights[n["q"]], weights[n["dkv"]]] + ([weights[n["g"]]] if self.gate is not None else [])
+        total = sum(r.shape[0] for r in rows)
+        if total % 8:
+            # rows of zeros, so that a token's projection is a whole number of 16-byte pieces and kernels may read it by them
+            rows.append(torch.zeros((8 - total % 8, self.hidden), dtype=rows[0].dtype))
         self.proj = Linear(compute_form(torch.cat(rows, dim=0), device, dtype), role="q_dkv_gate")
         self.out = Linear(compute_form(weights[n["o"]], device, dtype), ops.EPILOGUE_ACCUMULATE, role="o_proj")
         # per head: W_uk[h]^T [kv_rank, dim] (the query goes into the compressed space) and W_uv[h] [vdim, kv_rank]
@@ -73,6 +82,9 @@ class LatentAttention:
         self.uk_t = compute_form(uk, device, dtype)
         self.uv = compute_form(weights[n["uv"]].reshape(H, self.vdim, self.rank), device, dtype)
         self.c_gain = weights[n["cn"]].to(device).float().contiguous()
+        if self.rank % 8 == 0 and ops.latent_attention_expanded_supported(dtype, self.dim, self.rot, self.vdim):
+            # every head's key and value rows in one product over the latent vectors: [W_uk; W_uv]
+            self.ukv = Linear(compute_form(torch.cat([weights[n["uk"]], weights[n["uv"]]], dim=0), device, dtype), role="kv_expand")
         if self.position is not None:
             self.position.load(weights, device, dtype)
 
@@ -85,6 +97,11 @@ class LatentAttention:
         plane, _ = ctx.cache.plane(slot.group, slot.plane)
         table = ctx.cache.tables[slot.group]
         proj = self.proj(x, ctx=ctx)                                   # [T, queries | latent row | gate]
+        if (self.ukv is not None and not ctx.decode and ctx.max_new_tokens >= EXPAND_FROM_TOKENS and ctx.host_starts
+                and not any(ctx.host_starts)):
+            out = self._attend_expanded(proj, rotary, plane if slot.writes else None, table, ctx)
+            self._gate_and_project(out, proj, residual, ctx)
+            return
         q = torch.empty((T, H * dl), dtype=proj.dtype, device=proj.device)
         ops.latent_prep(proj, self.q_cols, q, plane if slot.writes else None, table, ctx.cache.block_tokens, ctx.token_seq,
                         ctx.token_pos, ctx.slot_ids, self.c_gain, rotary.inv_freq if rotary else None,
@@ -100,10 +117,28 @@ class LatentAttention:
         ops.tag = "v_up"
         matmul_batched(out, mixed, self.uv, self.rank, self.vdim)
         ops.tag = None
+        self._gate_and_project(out, proj, residual, ctx)
+
+    def _gate_and_project(self, out, proj, residual, ctx) -> None:
         if self.gate is not None:
-            g0 = self.q_cols + dl
-            ops.sigmoid_gate(out, proj[:, g0:g0 + self.gate_cols], H, self.vdim, self.gate == "head")
+            g0 = self.q_cols + self.rank + self.rot
+            ops.sigmoid_gate(out, proj[:, g0:g0 + self.gate_cols], self.heads, self.vdim, self.gate == "head")
         self.out.add_then_norm(out, residual, getattr(ctx, "norm_ahead", None), ctx)
+
+    def _attend_expanded(self, proj, rotary, plane, table, ctx) -> torch.Tensor:
+        """Whole prompts from position 0: the cache rows are written as always and also kept side by side; one product
+        makes every head's keys and values from them; the attention runs per head on the tensor cores."""
+        T, H = ctx.num_tokens, self.heads
+        rows = torch.empty((T, self.rank + self.rot), dtype=proj.dtype, device=proj.device)
+        ops.latent_prep(proj, self.q_cols, None, plane, table, ctx.cache.block_tokens, ctx.token_seq, ctx.token_pos, ctx.slot_ids,
+                        self.c_gain, rotary.inv_freq if rotary else None, rotary.rope_dim if rotary else 0,
+                        rotary.amplitude if rotary else 1.0, self.eps, H, self.dim, self.rot, self.rank, rows_out=rows)
+        kv = self.ukv(rows[:, :self.rank], ctx=ctx)                    # [T, H * dim | H * vdim]
+        out = torch.empty((T, H * self.vdim), dtype=proj.dtype, device=proj.device)
+        ops.latent_attention_expanded(out, proj[:, :self.q_cols], kv[:, :H * self.dim], kv[:, H * self.dim:], rows[:, self.rank:],
+                                      ctx.cu_seqlens, ctx.slot_ids, ctx.kv_lens, ctx.num_seqs, ctx.max_new_tokens, H, self.dim,
+                                      self.rot, self.vdim, self.scale, self.window)
+        return out
 
     def attend(self, out, q, plane, table, ctx) -> None:
         # bfloat16 with rows in pieces of 16: the tensor-core kernel; 32-bit and odd sizes: the general CUDA-core kernel

@@ -190,7 +190,7 @@ def _latent_part(hidden, heads, dim, rot, vdim, rank, scale, gate, dims=None, sc
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("hidden, heads, dim, rot, vdim, rank, gate, dims, scaling, window",
-                         [(42, 3, 10, 6, 9, 21, "element", 4, None, None), (64, 20, 16, 16, 24, 48, "head", None, YARN, None),
+                         [(42, 3, 10, 6, 9, 21, "element", 4, None, None), (64, 20, 16, 16, 32, 48, "head", None, YARN, None),
                           (48, 1, 32, 16, 16, 64, None, None, YARN, None), (40, 4, 8, 8, 8, 24, "head", None, None, 70)])
 def test_latent_attention_prompts_then_decoding(dtype, hidden, heads, dim, rot, vdim, rank, gate, dims, scaling, window):
     from hymt2sharp_b200.parts import MixerSlot
@@ -224,13 +224,13 @@ def test_latent_attention_finds_one_key_wherever_it_lies(dtype):
     token, the last and first rows of cache blocks (63 | 64), the edges of the decode kernel's chunks (255 | 256) and the
     token just before the query.  A kernel that misses or misplaces one key gives another token's value."""
     from hymt2sharp_b200.parts import MixerSlot
-    hidden, heads, dim, rot, vdim, rank = 48, 2, 24, 16, 12, 32      # (rows of 48 and 32: bfloat16 runs the tensor-core kernel)
+    hidden, heads, dim, rot, vdim, rank = 48, 2, 32, 16, 16, 32      # (pieces of 16 everywhere: bfloat16 runs the tensor-core kernels)
     part, mixer = _latent_part(hidden, heads, dim, rot, vdim, rank, 1.0, None)
     w = _weights(part.tensors(), 0.3, seed=3)
     w["dkv.norm"] = torch.ones(rank).to(torch.bfloat16)
     pairs = {330: 0, 331: 63, 332: 64, 333: 255, 334: 256, 335: 1, 336: 127, 337: 128, 338: 319, 339: 320, 340: 339, 200: 3, 129: 64}
     q0 = w["q"].to(F64).reshape(heads, dim + rot, hidden) * 0.05
-    for seed in range(40):       # (a random key may happen to lie better than the planted one: the first draw without such a key)
+    for seed in range(300):      # (a random key may happen to lie nearly as well as the planted one: the first draw without such a key)
         gen = torch.Generator().manual_seed(seed)
         R = torch.linalg.qr(torch.randn(hidden, hidden, generator=gen, dtype=F64))[0]
         x = torch.randn(341, hidden, generator=gen, dtype=F64)
@@ -239,14 +239,14 @@ def test_latent_attention_finds_one_key_wherever_it_lies(dtype):
         x = x.to(torch.bfloat16).float()
         q = q0.clone()
         for h in range(heads):
-            q[h, :dim] = 4.0 * w["uk"].to(F64)[h * dim:(h + 1) * dim] @ w["dkv"].to(F64)[:rank] @ R
+            q[h, :dim] = 6.0 * w["uk"].to(F64)[h * dim:(h + 1) * dim] @ w["dkv"].to(F64)[:rank] @ R
         w["q"] = q.reshape(heads * (dim + rot), hidden).to(torch.bfloat16)
         wf = {k: v.to(F64) for k, v in w.items()}
         p = plain.latent_attention(x.to(F64), wf, mixer, None, 1e-5, return_weights=True)
-        if all(float(p[:, t, s].min()) > 0.8 for t, s in pairs.items()):
+        if all(float(p[:, t, s].min()) > 0.97 for t, s in pairs.items()):
             break
     for t, s in pairs.items():
-        assert float(p[:, t, s].min()) > 0.8, (t, s, p[:, t, s])
+        assert float(p[:, t, s].min()) > 0.97, (t, s, p[:, t, s])
     part.load(w, DEV, dtype)
     ref = plain.latent_attention(x.to(F64), wf, mixer, None, 1e-5)
     cache = _cache(dtype, part.cache_need())
@@ -265,7 +265,7 @@ def test_latent_attention_finds_one_key_wherever_it_lies(dtype):
 def test_latent_attention_window_edge(dtype):
     """With a window of 50 the key 50 back is out and the key 49 back is in: each probe's query is built to meet one of them."""
     from hymt2sharp_b200.parts import MixerSlot
-    hidden, heads, dim, rot, vdim, rank, window = 32, 2, 16, 16, 8, 32, 50
+    hidden, heads, dim, rot, vdim, rank, window = 32, 2, 16, 16, 16, 32, 50
     part, mixer = _latent_part(hidden, heads, dim, rot, vdim, rank, 1.0, None, window=window)
     w = _weights(part.tensors(), 0.3, seed=4)
     gen = torch.Generator().manual_seed(2)
