@@ -188,6 +188,10 @@ attention_simt_kernel(AttnParams p) {
     }
 }
 
+constexpr int MERGE_WEIGHTS = 128, MERGE_COLS = 4;
+
+inline int merge_threads(int dv) { return dv > 256 ? 256 : (dv > 128 ? 128 : 64); }
+
 // out[row] = sum_s acc_s * exp(m_s - M) / sum_s l_s * exp(m_s - M), chunks in index order.
 template <typename T>
 __global__ void attention_merge_kernel(AttnParams p, int total_tokens) {
@@ -215,10 +219,40 @@ __global__ void attention_merge_kernel(AttnParams p, int total_tokens) {
     for (int s = s_begin; s < s_end; s++) L += ml[2 * s + 1] * expf(ml[2 * s] - M);
     const float inv = L > 0.f ? 1.0f / L : 0.f;
     const float* pa = p.part_acc + (size_t)row * p.max_splits * p.dv;
+    // the chunks' weights once for the row (in pieces of MERGE_WEIGHTS chunks), not once per output entry
+    __shared__ float weight[MERGE_WEIGHTS];
+    float a[MERGE_COLS];
+#pragma unroll
+    for (int i = 0; i < MERGE_COLS; i++) a[i] = 0.f;
+    const bool fits = p.dv <= MERGE_COLS * (int)blockDim.x;
+    for (int s0 = s_begin; s0 < s_end; s0 += MERGE_WEIGHTS) {
+        const int s1 = min(s_end, s0 + MERGE_WEIGHTS);
+        __syncthreads();
+        for (int s = s0 + threadIdx.x; s < s1; s += blockDim.x) weight[s - s0] = expf(ml[2 * s] - M);
+        __syncthreads();
+        if (fits) {
+            for (int s = s0; s < s1; s++) {
+                const float w = weight[s - s0];
+#pragma unroll
+                for (int i = 0; i < MERGE_COLS; i++) {
+                    const int x = threadIdx.x + i * blockDim.x;
+                    if (x < p.dv) a[i] = fmaf(pa[(size_t)s * p.dv + x], w, a[i]);
+                }
+            }
+        }
+    }
+    if (fits) {
+#pragma unroll
+        for (int i = 0; i < MERGE_COLS; i++) {
+            const int x = threadIdx.x + i * blockDim.x;
+            if (x < p.dv) ((T*)p.out)[(size_t)row * p.dv + x] = from_float<T>(a[i] * inv);
+        }
+        return;
+    }
     for (int x = threadIdx.x; x < p.dv; x += blockDim.x) {
-        float a = 0.f;
-        for (int s = s_begin; s < s_end; s++) a = fmaf(pa[(size_t)s * p.dv + x], expf(ml[2 * s] - M), a);
-        ((T*)p.out)[(size_t)row * p.dv + x] = from_float<T>(a * inv);
+        float acc = 0.f;
+        for (int s = s_begin; s < s_end; s++) acc = fmaf(pa[(size_t)s * p.dv + x], expf(ml[2 * s] - M), acc);
+        ((T*)p.out)[(size_t)row * p.dv + x] = from_float<T>(acc * inv);
     }
 }
 
@@ -234,7 +268,7 @@ int hymt2_attention_merge_launch(void* out, int dtype, const int* cu_seqlens, co
     p.out = out; p.cu_seqlens = cu_seqlens; p.slot_ids = slot_ids; p.kv_lens = kv_lens;
     p.part_acc = part_acc; p.part_ml = part_ml; p.nh = nh; p.d = d; p.dv = d; p.window = window;
     p.split_keys = split_keys; p.max_splits = max_splits;
-    HYMT2_DISPATCH_DTYPE(dtype, T, (attention_merge_kernel<T><<<tokens * nh, 64, 0, stream>>>(p, tokens)));
+    HYMT2_DISPATCH_DTYPE(dtype, T, (attention_merge_kernel<T><<<tokens * nh, merge_threads(d), 0, stream>>>(p, tokens)));
     return hymt2_check_launch("attention_merge");
 }
 
@@ -289,7 +323,7 @@ static int attention_simt_general(void* out, const void* q, const void* k_cache,
         kernel<<<grid, ROWS * LANES_PER_ROW, smem, stream>>>(p);
         rc = hymt2_check_launch("attention_simt");
         if (rc == HYMT2_OK && split_keys > 0) {
-            attention_merge_kernel<T><<<tokens * nh, 64, 0, stream>>>(p, tokens);
+            attention_merge_kernel<T><<<tokens * nh, merge_threads(dv), 0, stream>>>(p, tokens);
             rc = hymt2_check_launch("attention_merge");
         }
     });

@@ -33,6 +33,15 @@ typedef __nv_bfloat16 bf16;
 
 constexpr int MT = 64, NT = 64, THREADS = 256, S_LD = 68, P_LD = 72;
 
+// 16 bytes from global to shared memory without a stop in registers; `valid` false: 16 zero bytes (nothing is read, the
+// address only has to be one that exists).  A tile's copies are all issued before any is waited for.
+__device__ __forceinline__ void copy16_async(void* smem, const void* gmem, bool valid) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    const int bytes = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(s), "l"(gmem), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void copies_wait() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
 struct LatentMmaParams {
     const bf16* q;        // [T * nh, d]
     bf16* out;            // [T * nh, dv]
@@ -74,7 +83,8 @@ latent_attention_mma_kernel(LatentMmaParams p) {
     if (slot < 0) return;
     const int tok0 = p.cu_seqlens[b], n = p.cu_seqlens[b + 1] - tok0;
     const int kv_len = p.kv_lens[b], start = kv_len - n;
-    const int rows_total = EXPANDED ? n : n * p.nh, r0 = blockIdx.x * MT;
+    // (the tiles with the most keys first: a sequence's last rows see all of it)
+    const int rows_total = EXPANDED ? n : n * p.nh, r0 = (int)(gridDim.x - 1 - blockIdx.x) * MT;
     if (r0 >= rows_total) return;
     const int rows_valid = min(MT, rows_total - r0);
     const int first_tok = EXPANDED ? r0 : r0 / p.nh, last_tok = EXPANDED ? r0 + rows_valid - 1 : (r0 + rows_valid - 1) / p.nh;
@@ -94,15 +104,20 @@ latent_attention_mma_kernel(LatentMmaParams p) {
     const size_t q_ld = EXPANDED ? (size_t)p.ldq_g : (size_t)d;
     for (int i = tid * 8; i < MT * d; i += THREADS * 8) {
         const int r = i / d, c = i - r * d;
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (r < rows_valid) v = *reinterpret_cast<const uint4*>(qg + (size_t)r * q_ld + c);
-        *reinterpret_cast<uint4*>(Qs + r * ldq + c) = v;
+        const bool ok = r < rows_valid;
+        copy16_async(Qs + r * ldq + c, qg + (ok ? (size_t)r * q_ld + c : 0), ok);
     }
     if (tid < MT) { m_s[tid] = -INFINITY; l_s[tid] = 0.f; corr_s[tid] = 1.f; }
 
     // which row of its 16 each entry of an accumulator fragment belongs to
-    const int rf_o = warp & 3, cf_o = warp >> 2;            // this warp's row fragment of O, and its first column fragment
-    float* stage = Ss + rf_o * 16 * S_LD + cf_o * 16;       // a 16x16 float32 patch of S that only this warp touches outside the S phase
+    // A tile of at most 16 live rows (a decode step's heads) is `narrow`: all warps share the one live row fragment and
+    // divide the columns among themselves; otherwise a warp owns one of four row fragments and every second column fragment.
+    const bool narrow = rows_valid <= 16;
+    const int rf_o = narrow ? 0 : warp & 3;                 // this warp's row fragment of O,
+    const int cf_o = narrow ? warp : warp >> 2;             // its first column fragment
+    const int cf_step = narrow ? 8 : 2;                     // and the distance to its next
+    const int o_col_frags = dv >> 4;
+    float* stage = Ss + (warp & 3) * 16 * S_LD + (warp >> 2) * 16;   // a 16x16 float32 patch of S that only this warp touches outside the S phase
     int row_of[8];
     {
         for (int i = lane; i < 256; i += 32) stage[(i >> 4) * S_LD + (i & 15)] = (float)(i >> 4);
@@ -112,13 +127,13 @@ latent_attention_mma_kernel(LatentMmaParams p) {
 #pragma unroll
         for (int e = 0; e < 8; e++) row_of[e] = (int)probe.x[e];
     }
-    const int o_frags_total = 4 * (dv >> 4);                // fragments of O; this warp owns warp, warp + 8, ...: row fragment rf_o,
-    wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc[MAXF];   // column fragments cf_o, cf_o + 2, ...
+    wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc[MAXF];   // O: row fragment rf_o, column fragments cf_o + i * cf_step
 #pragma unroll
     for (int i = 0; i < MAXF; i++) wmma::fill_fragment(acc[i], 0.f);
     const bool o_rows_live = rf_o * 16 < rows_valid;
-    const int rf_s = warp >> 1, cf_s = (warp & 1) * 2;      // this warp's part of S: row fragment rf_s, column fragments cf_s, cf_s + 1
-    const bool s_rows_live = rf_s * 16 < rows_valid;
+    // this warp's part of S: row fragment rf_s, column fragments cf_s, cf_s + 1 (narrow: warps 0..3 take one column fragment each)
+    const int rf_s = narrow ? 0 : warp >> 1, cf_s = narrow ? warp : (warp & 1) * 2;
+    const bool s_rows_live = narrow ? warp < 4 : rf_s * 16 < rows_valid;
 
     const int* table = p.block_table + (size_t)slot * p.table_stride;
     for (int k0 = (key_begin / NT) * NT; k0 < key_end; k0 += NT) {
@@ -128,17 +143,14 @@ latent_attention_mma_kernel(LatentMmaParams p) {
             const size_t t0 = (size_t)tok0 + k0;
             for (int i = tid * 8; i < NT * d; i += THREADS * 8) {
                 const int r = i / d, c = i - r * d;
-                uint4 v = make_uint4(0u, 0u, 0u, 0u);
-                if (r < keys_here)
-                    v = c < p.dim ? *reinterpret_cast<const uint4*>(p.kexp + (t0 + r) * p.ld_kexp + (size_t)head * p.dim + c)
-                                  : *reinterpret_cast<const uint4*>(p.krot + (t0 + r) * p.ld_krot + (c - p.dim));
-                *reinterpret_cast<uint4*>(Ks + r * ldq + c) = v;
+                const bool ok = r < keys_here;
+                const size_t t = t0 + (ok ? r : 0);
+                copy16_async(Ks + r * ldq + c, c < p.dim ? p.kexp + t * p.ld_kexp + (size_t)head * p.dim + c : p.krot + t * p.ld_krot + (c - p.dim), ok);
             }
             for (int i = tid * 8; i < NT * dv; i += THREADS * 8) {
                 const int r = i / dv, c = i - r * dv;
-                uint4 v = make_uint4(0u, 0u, 0u, 0u);
-                if (r < keys_here) v = *reinterpret_cast<const uint4*>(p.vexp + (t0 + r) * p.ld_vexp + (size_t)head * dv + c);
-                *reinterpret_cast<uint4*>(Vs + r * ldv + c) = v;
+                const bool ok = r < keys_here;
+                copy16_async(Vs + r * ldv + c, p.vexp + (t0 + (ok ? r : 0)) * p.ld_vexp + (size_t)head * dv + c, ok);
             }
         } else {
             const int block = table[k0 / NT];
@@ -146,11 +158,11 @@ latent_attention_mma_kernel(LatentMmaParams p) {
             const int keys_here = block < 0 ? 0 : min(NT, kv_len - k0);   // rows past the sequence's end hold anything: they are zeroed
             for (int i = tid * 8; i < NT * d; i += THREADS * 8) {
                 const int r = i / d, c = i - r * d;
-                uint4 v = make_uint4(0u, 0u, 0u, 0u);
-                if (r < keys_here) v = *reinterpret_cast<const uint4*>(kg + i);
-                *reinterpret_cast<uint4*>(Ks + r * ldq + c) = v;
+                const bool ok = r < keys_here;
+                copy16_async(Ks + r * ldq + c, kg + (ok ? i : 0), ok);
             }
         }
+        copies_wait();
         __syncthreads();
 
         // S = Q K^T
@@ -166,12 +178,14 @@ latent_attention_mma_kernel(LatentMmaParams p) {
                 wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::col_major> b0, b1;
                 wmma::load_matrix_sync(a, qa + kk, ldq);
                 wmma::load_matrix_sync(b0, kb0 + kk, ldq);
-                wmma::load_matrix_sync(b1, kb1 + kk, ldq);
                 wmma::mma_sync(s0, a, b0, s0);
-                wmma::mma_sync(s1, a, b1, s1);
+                if (!narrow) {
+                    wmma::load_matrix_sync(b1, kb1 + kk, ldq);
+                    wmma::mma_sync(s1, a, b1, s1);
+                }
             }
             wmma::store_matrix_sync(Ss + rf_s * 16 * S_LD + cf_s * 16, s0, S_LD, wmma::mem_row_major);
-            wmma::store_matrix_sync(Ss + rf_s * 16 * S_LD + cf_s * 16 + 16, s1, S_LD, wmma::mem_row_major);
+            if (!narrow) wmma::store_matrix_sync(Ss + rf_s * 16 * S_LD + cf_s * 16 + 16, s1, S_LD, wmma::mem_row_major);
         }
         __syncthreads();
 
@@ -229,7 +243,7 @@ latent_attention_mma_kernel(LatentMmaParams p) {
             for (int e = 0; e < 8; e++) f[e] = corr_s[rf_o * 16 + row_of[e]];
 #pragma unroll
             for (int i = 0; i < MAXF; i++)
-                if (warp + 8 * i < o_frags_total) {
+                if (cf_o + cf_step * i < o_col_frags) {
 #pragma unroll
                     for (int e = 0; e < 8; e++) acc[i].x[e] *= f[e];
                 }
@@ -239,9 +253,9 @@ latent_attention_mma_kernel(LatentMmaParams p) {
                 wmma::load_matrix_sync(a, Ps + rf_o * 16 * P_LD + kk, P_LD);
 #pragma unroll
                 for (int i = 0; i < MAXF; i++)
-                    if (warp + 8 * i < o_frags_total) {
+                    if (cf_o + cf_step * i < o_col_frags) {
                         wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::row_major> vb;
-                        wmma::load_matrix_sync(vb, (EXPANDED ? Vs : Ks) + kk * ldv + (cf_o + 2 * i) * 16, ldv);
+                        wmma::load_matrix_sync(vb, (EXPANDED ? Vs : Ks) + kk * ldv + (cf_o + cf_step * i) * 16, ldv);
                         wmma::mma_sync(acc[i], a, vb, acc[i]);
                     }
             }
@@ -264,13 +278,13 @@ latent_attention_mma_kernel(LatentMmaParams p) {
     }
 #pragma unroll
     for (int i = 0; i < MAXF; i++) {
-        if (warp + 8 * i >= o_frags_total) continue;
+        if (cf_o + cf_step * i >= o_col_frags) continue;
 #pragma unroll
         for (int e = 0; e < 8; e++) acc[i].x[e] *= f[e];
         wmma::store_matrix_sync(stage, acc[i], S_LD, wmma::mem_row_major);
         __syncwarp();
         const int r = lane >> 1, c8 = (lane & 1) * 8;
-        const int row = rf_o * 16 + r, col = (cf_o + 2 * i) * 16 + c8;
+        const int row = rf_o * 16 + r, col = (cf_o + cf_step * i) * 16 + c8;
         if (row < rows_valid) {
             const float* src = stage + r * S_LD + c8;
             if (split_mode) {

@@ -7,7 +7,7 @@
 
 namespace {
 
-constexpr int CONV_MAX_TAPS = 16, CONV_CHUNK = 32, CONV_THREADS = 128;
+constexpr int CONV_MAX_TAPS = 16, CONV_CHUNK = 16, CONV_THREADS = 128;
 
 struct ConvParams {
     const void* x;        // [T, ldx] the inputs (channel c of token t at x[t * ldx + c])
@@ -45,7 +45,7 @@ template <typename T, int V> __device__ __forceinline__ void store_chan(T* p, co
 }
 
 // A thread owns V neighbouring channels (V = 2 where the rows allow 4- or 8-byte accesses).
-template <typename T, int V>
+template <typename T, int V, int MAXT>
 __global__ void __launch_bounds__(CONV_THREADS)
 causal_conv_kernel(ConvParams p) {
     pdl_wait();   // everything in front is complete before anything is read; then the next kernel may be set up meanwhile
@@ -70,14 +70,14 @@ causal_conv_kernel(ConvParams p) {
     const int start = p.kv_lens[b] - n;   // position of the step's first token
     const int taps = p.taps, hist = taps - 1;
     float* st = (float*)(p.state + (size_t)slot * p.state_stride) + c;   // st[j * channels], j = 0 oldest
-    float w[CONV_MAX_TAPS][V], win[CONV_MAX_TAPS][V];
+    float w[MAXT][V], win[MAXT][V];
 #pragma unroll
-    for (int j = 0; j < CONV_MAX_TAPS; j++)
+    for (int j = 0; j < MAXT; j++)
 #pragma unroll
         for (int k = 0; k < V; k++) w[j][k] = j < taps ? p.w[(size_t)(c + k) * taps + j] : 0.f;
     // win[j] for j < hist: the input at index i0 - hist + j among the new tokens
 #pragma unroll
-    for (int j = 0; j < CONV_MAX_TAPS; j++) {
+    for (int j = 0; j < MAXT; j++) {
 #pragma unroll
         for (int k = 0; k < V; k++) win[j][k] = 0.f;
         if (j < hist) {
@@ -99,10 +99,10 @@ causal_conv_kernel(ConvParams p) {
         for (int k = 0; k < V; k++) {
             float a = 0.f;
 #pragma unroll
-            for (int j = 0; j < CONV_MAX_TAPS; j++)
+            for (int j = 0; j < MAXT; j++)
                 if (j < hist) a = fmaf(w[j][k], win[j][k], a);
 #pragma unroll
-            for (int j = 0; j < CONV_MAX_TAPS; j++)
+            for (int j = 0; j < MAXT; j++)
                 if (j == hist) a = fmaf(w[j][k], cur[k], a);
             a += bias[k];
             if (p.add_input) a += cur[k];
@@ -110,13 +110,13 @@ causal_conv_kernel(ConvParams p) {
         }
         store_chan<T, V>(out + (size_t)i * p.ldo, acc);
 #pragma unroll
-        for (int j = 0; j < CONV_MAX_TAPS - 1; j++)
+        for (int j = 0; j < MAXT - 1; j++)
             if (j + 1 < hist) {
 #pragma unroll
                 for (int k = 0; k < V; k++) win[j][k] = win[j + 1][k];
             }
 #pragma unroll
-        for (int j = 0; j < CONV_MAX_TAPS; j++)
+        for (int j = 0; j < MAXT; j++)
             if (j == hist - 1) {
 #pragma unroll
                 for (int k = 0; k < V; k++) win[j][k] = cur[k];
@@ -292,12 +292,15 @@ HYMT2_API int hymt2_causal_conv(void* out, const void* x, int dtype, const float
     HYMT2_REQUIRE(chunks <= 65535, "causal_conv: %d tokens in one sequence are too many for one launch", max_new_tokens);
     HYMT2_DISPATCH_DTYPE(dtype, T, {
         const bool pairs = channels % 2 == 0 && ldx % 2 == 0 && ldo % 2 == 0 && (uintptr_t)x % (2 * sizeof(T)) == 0 && (uintptr_t)out % (2 * sizeof(T)) == 0;
+        // (the window of inputs lives in registers: a kernel for filters of up to 4 taps, one for up to 16)
         if (pairs) {
             const dim3 grid((channels / 2 + CONV_THREADS - 1) / CONV_THREADS, chunks, batch);
-            launch_pdl(causal_conv_kernel<T, 2>, grid, dim3(CONV_THREADS), 0, stream, p);
+            if (taps <= 4) launch_pdl(causal_conv_kernel<T, 2, 4>, grid, dim3(CONV_THREADS), 0, stream, p);
+            else launch_pdl(causal_conv_kernel<T, 2, CONV_MAX_TAPS>, grid, dim3(CONV_THREADS), 0, stream, p);
         } else {
             const dim3 grid((channels + CONV_THREADS - 1) / CONV_THREADS, chunks, batch);
-            launch_pdl(causal_conv_kernel<T, 1>, grid, dim3(CONV_THREADS), 0, stream, p);
+            if (taps <= 4) launch_pdl(causal_conv_kernel<T, 1, 4>, grid, dim3(CONV_THREADS), 0, stream, p);
+            else launch_pdl(causal_conv_kernel<T, 1, CONV_MAX_TAPS>, grid, dim3(CONV_THREADS), 0, stream, p);
         }
     });
     return hymt2_check_launch("causal_conv");

@@ -28,7 +28,8 @@ from .linear import Linear, compute_form, matmul_batched
 
 EXPAND_FROM_TOKENS = 32   # prompts from this length on are worth one more product (keys and values per head)
 SPLIT_KEYS = 256     # decode: keys per partial, a constant so that the cut depends on nothing else
-SPLIT_KEYS_TC = 128  # the same for the tensor-core kernel, whose blocks are few and large: more of them per sequence
+SPLIT_KEYS_TC = 128  # the same for the tensor-core kernel, whose blocks are few and large: two tiles of keys each (one tile each
+                     # measured slower: twice the partials to write and fold)
 
 
 class LatentAttention:

@@ -67,7 +67,8 @@ class Linear:
         self(x, out=residual)
 
 
-TC_BATCH_MIN_TOKENS = 128   # from this many tokens on, a batch of small products goes to the tensor cores one by one
+TC_BATCH_MIN_TOKENS = 128   # from this many tokens on, a batch of small products goes to the tensor cores one by one,
+TC_BATCH_MIN_WEIGHT = 256 * 256   # if each of them is large enough to be worth a launch of its own (entries of w[z])
 
 
 def matmul_batched(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, x_step: int, out_step: int) -> None:
@@ -79,7 +80,7 @@ def matmul_batched(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, x_step: 
     if x.shape[0] <= ops.SKINNY_MAX_ROWS and x.dtype == w.dtype:
         ops.gemm_skinny_batched(out, x, w, x_step, out_step)
         return
-    if x.shape[0] >= TC_BATCH_MIN_TOKENS and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
+    if x.shape[0] >= TC_BATCH_MIN_TOKENS and N * K >= TC_BATCH_MIN_WEIGHT and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
         views = [(out[:, z * out_step: z * out_step + N], x[:, z * x_step: z * x_step + K], w[z]) for z in range(batch)]
         if all(ops.gemm_tc_supported(o, a, b, ops.EPILOGUE_STORE) for o, a, b in views[:2]) and (x_step * 2) % 16 == 0:
             for o, a, b in views:
