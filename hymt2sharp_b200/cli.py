@@ -83,8 +83,12 @@ def main(argv=None) -> int:
     t0 = time.perf_counter()
     engine = Engine(args.model, dtype=args.dtype, max_tokens=args.max_context, max_batch=args.max_batch)
     c = engine.config
-    print(f"arch={c.architecture} layers={c.num_hidden_layers} hidden={c.hidden_size} "
-          f"heads={c.num_attention_heads}/{c.num_key_value_heads} vocab={c.vocab_size}  "
+    if hasattr(c, "num_attention_heads"):
+        mixers = f"heads={c.num_attention_heads}/{c.num_key_value_heads}"
+    else:   # a design that chooses its mixer layer by layer: how many layers of each kind
+        kinds = [layer.type for layer in c.layers]
+        mixers = "mixers=" + ",".join(f"{k}x{kinds.count(k)}" for k in dict.fromkeys(kinds))
+    print(f"arch={c.architecture} layers={c.num_hidden_layers} hidden={c.hidden_size} {mixers} vocab={c.vocab_size}  "
           f"(loaded in {time.perf_counter() - t0:.1f} s)")
     sampling = SamplingParams(temperature=args.temperature, top_k=args.top_k, top_p=args.top_p, min_p=args.min_p,
                               repeat_penalty=args.repeat_penalty, penalty_window=args.penalty_window, seed=args.seed)

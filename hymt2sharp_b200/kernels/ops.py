@@ -1086,3 +1086,4 @@ def latent_attention_expanded(out: torch.Tensor, q: torch.Tensor, kexp: torch.Te
                                                   c_long(krot.stride(0)), _ptr(cu_seqlens), _ptr(slot_ids), _ptr(kv_lens), c_int(batch),
                                                   c_int(max_new_tokens), c_int(nh), c_int(dim), c_int(rot), c_int(dv), c_float(scale),
                                                   c_int(window), _stream()), "latent_attention_expanded")
+

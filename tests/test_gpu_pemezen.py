@@ -176,3 +176,19 @@ def test_a_state_model_is_reset_but_not_cut(engines):
     b = eng.step([StepEntry(slot, toks, [19])]).cpu().numpy()
     eng.free_slots([slot])
     assert np.array_equal(a, b)
+
+
+def test_command_line_runs_the_design(folders, oracles, capsys, tmp_path):
+    """python -m hymt2sharp_b200 on a Pemezen folder, and --random from a configuration file of the design."""
+    import json
+    from hymt2sharp_b200 import cli
+    cfg, w = oracles["odd"]
+    assert cli.main(["--model", folders["odd"], "--dtype", "float32", "--prompt", "5 17 3 60", "--max-tokens", "5"]) == 0
+    out = capsys.readouterr().out
+    assert "arch=Pemezen layers=4 hidden=42 mixers=rglrux2,latent_attentionx1,latent_attention_2x1 vocab=97" in out
+    want = plain.greedy(cfg, w, [5, 17, 3, 60], 6)
+    assert "Assistant: " + ",".join(map(str, want)) in out
+    (tmp_path / "c.json").write_text(json.dumps(pemezen_models.CONFIGS["even"]["config"]))
+    assert cli.main(["--model", str(tmp_path / "m"), "--random", str(tmp_path / "c.json"), "--weights-seed", "3", "--sigma", "0.05",
+                     "--prompt", "1 2 3", "--max-tokens", "3"]) == 0
+    assert "arch=Pemezen layers=3 hidden=128" in capsys.readouterr().out

@@ -191,7 +191,8 @@ def _latent_part(hidden, heads, dim, rot, vdim, rank, scale, gate, dims=None, sc
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("hidden, heads, dim, rot, vdim, rank, gate, dims, scaling, window",
                          [(42, 3, 10, 6, 9, 21, "element", 4, None, None), (64, 20, 16, 16, 32, 48, "head", None, YARN, None),
-                          (48, 1, 32, 16, 16, 64, None, None, YARN, None), (40, 4, 8, 8, 8, 24, "head", None, None, 70)])
+                          (48, 1, 32, 16, 16, 64, None, None, YARN, None), (40, 4, 8, 8, 8, 24, "head", None, None, 70),
+                          (64, 2, 192, 32, 144, 64, "element", 16, None, None), (64, 3, 48, 16, 32, 32, "head", None, None, 90)])
 def test_latent_attention_prompts_then_decoding(dtype, hidden, heads, dim, rot, vdim, rank, gate, dims, scaling, window):
     from hymt2sharp_b200.parts import MixerSlot
     part, mixer = _latent_part(hidden, heads, dim, rot, vdim, rank, 0.4, gate, dims, scaling, window)
