@@ -102,10 +102,16 @@ latent_attention_mma_kernel(LatentMmaParams p) {
     // the queries
     const bf16* qg = EXPANDED ? p.q + (size_t)(tok0 + r0) * p.ldq_g + (size_t)head * d : p.q + row_base * d;
     const size_t q_ld = EXPANDED ? (size_t)p.ldq_g : (size_t)d;
-    for (int i = tid * 8; i < MT * d; i += THREADS * 8) {
-        const int r = i / d, c = i - r * d;
+    // A thread's 16-byte pieces of a [rows][d] tile are THREADS * 8 entries apart: row and column move on by fixed
+    // steps (one division for the kernel, none per piece).
+    const int step_r = (THREADS * 8) / d, step_c = (THREADS * 8) - step_r * d;
+    const int first_r = (tid * 8) / d, first_c = tid * 8 - first_r * d;
+    const int q_rows = min(MT, (rows_valid + 15) & ~15);   // whole row fragments that hold a live row; the others are never read
+    for (int r = first_r, c = first_c; r < q_rows;) {
         const bool ok = r < rows_valid;
         copy16_async(Qs + r * ldq + c, qg + (ok ? (size_t)r * q_ld + c : 0), ok);
+        r += step_r; c += step_c;
+        if (c >= d) { c -= d; r++; }
     }
     if (tid < MT) { m_s[tid] = -INFINITY; l_s[tid] = 0.f; corr_s[tid] = 1.f; }
 
@@ -132,8 +138,13 @@ latent_attention_mma_kernel(LatentMmaParams p) {
     for (int i = 0; i < MAXF; i++) wmma::fill_fragment(acc[i], 0.f);
     const bool o_rows_live = rf_o * 16 < rows_valid;
     // this warp's part of S: row fragment rf_s, column fragments cf_s, cf_s + 1 (narrow: warps 0..3 take one column fragment each)
-    const int rf_s = narrow ? 0 : warp >> 1, cf_s = narrow ? warp : (warp & 1) * 2;
-    const bool s_rows_live = narrow ? warp < 4 : rf_s * 16 < rows_valid;
+    // In the narrow layout warps 0..3 sum over the first half of a key's entries and warps 4..7 over the second half, into rows
+    // 16..31 of S; the softmax adds the two.
+    const int rf_s = narrow ? 0 : warp >> 1, cf_s = narrow ? (warp & 3) : (warp & 1) * 2;
+    const bool s_rows_live = narrow ? true : rf_s * 16 < rows_valid;
+    const int kk_half = ((d >> 4) + 1) >> 1 << 4;   // entries that the first half takes (whole pieces of 16)
+    const int kk_begin = narrow && warp >= 4 ? kk_half : 0, kk_end = narrow && warp < 4 ? kk_half : d;
+    const int s_row0 = narrow && warp >= 4 ? 16 : rf_s * 16;
 
     const int* table = p.block_table + (size_t)slot * p.table_stride;
     for (int k0 = (key_begin / NT) * NT; k0 < key_end; k0 += NT) {
@@ -141,11 +152,12 @@ latent_attention_mma_kernel(LatentMmaParams p) {
         if (EXPANDED) {
             const int keys_here = min(NT, n - k0);   // (the sequence starts in this step: its keys are its new tokens)
             const size_t t0 = (size_t)tok0 + k0;
-            for (int i = tid * 8; i < NT * d; i += THREADS * 8) {
-                const int r = i / d, c = i - r * d;
+            for (int r = first_r, c = first_c; r < NT;) {
                 const bool ok = r < keys_here;
                 const size_t t = t0 + (ok ? r : 0);
                 copy16_async(Ks + r * ldq + c, c < p.dim ? p.kexp + t * p.ld_kexp + (size_t)head * p.dim + c : p.krot + t * p.ld_krot + (c - p.dim), ok);
+                r += step_r; c += step_c;
+                if (c >= d) { c -= d; r++; }
             }
             for (int i = tid * 8; i < NT * dv; i += THREADS * 8) {
                 const int r = i / dv, c = i - r * dv;
@@ -156,10 +168,11 @@ latent_attention_mma_kernel(LatentMmaParams p) {
             const int block = table[k0 / NT];
             const bf16* kg = p.cache + (size_t)(block < 0 ? 0 : block) * NT * d;
             const int keys_here = block < 0 ? 0 : min(NT, kv_len - k0);   // rows past the sequence's end hold anything: they are zeroed
-            for (int i = tid * 8; i < NT * d; i += THREADS * 8) {
-                const int r = i / d, c = i - r * d;
+            for (int r = first_r, c = first_c; r < NT;) {
                 const bool ok = r < keys_here;
-                copy16_async(Ks + r * ldq + c, kg + (ok ? i : 0), ok);
+                copy16_async(Ks + r * ldq + c, kg + (ok ? (size_t)r * d + c : 0), ok);
+                r += step_r; c += step_c;
+                if (c >= d) { c -= d; r++; }
             }
         }
         copies_wait();
@@ -173,7 +186,7 @@ latent_attention_mma_kernel(LatentMmaParams p) {
             const bf16* qa = Qs + rf_s * 16 * ldq;
             const bf16* kb0 = Ks + cf_s * 16 * ldq;
             const bf16* kb1 = kb0 + 16 * ldq;
-            for (int kk = 0; kk < d; kk += 16) {
+            for (int kk = kk_begin; kk < kk_end; kk += 16) {
                 wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> a;
                 wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::col_major> b0, b1;
                 wmma::load_matrix_sync(a, qa + kk, ldq);
@@ -184,13 +197,13 @@ latent_attention_mma_kernel(LatentMmaParams p) {
                     wmma::mma_sync(s1, a, b1, s1);
                 }
             }
-            wmma::store_matrix_sync(Ss + rf_s * 16 * S_LD + cf_s * 16, s0, S_LD, wmma::mem_row_major);
-            if (!narrow) wmma::store_matrix_sync(Ss + rf_s * 16 * S_LD + cf_s * 16 + 16, s1, S_LD, wmma::mem_row_major);
+            wmma::store_matrix_sync(Ss + s_row0 * S_LD + cf_s * 16, s0, S_LD, wmma::mem_row_major);
+            if (!narrow) wmma::store_matrix_sync(Ss + s_row0 * S_LD + cf_s * 16 + 16, s1, S_LD, wmma::mem_row_major);
         }
         __syncthreads();
 
-        // the online softmax: four threads a row, 16 keys each
-        {
+        // the online softmax: four threads a row, 16 keys each (narrow: the 16 live rows only)
+        if (!narrow || tid < 64) {
             const int r = tid >> 2, part = tid & 3;
             const int grow = r0 + r;
             const bool row_ok = r < rows_valid;
@@ -202,7 +215,8 @@ latent_attention_mma_kernel(LatentMmaParams p) {
             for (int j = 0; j < 16; j++) {
                 const int key = k0 + part * 16 + j;
                 const bool visible = row_ok && key >= lo && key <= pos && key >= key_begin && key < key_end;
-                s[j] = visible ? Ss[r * S_LD + part * 16 + j] * p.scale : -INFINITY;
+                const float sum = narrow ? Ss[r * S_LD + part * 16 + j] + Ss[(16 + r) * S_LD + part * 16 + j] : Ss[r * S_LD + part * 16 + j];
+                s[j] = visible ? sum * p.scale : -INFINITY;
                 tmax = fmaxf(tmax, s[j]);
             }
             tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));

@@ -23,7 +23,7 @@ def build_spec(cfg: PemezenConfig) -> ModelSpec:
     def norm(name: str) -> PartSpec:
         return PartSpec("rmsnorm", dict(dim=H, eps=cfg.norm_eps, weight=name, groups=cfg.norm_groups))
 
-    layers = []
+    layers, unread = [], []
     for i, layer in enumerate(cfg.layers):
         p, m = f"l{i}.", layer.mixer
         x = p + "mix."
@@ -46,9 +46,12 @@ def build_spec(cfg: PemezenConfig) -> ModelSpec:
                                                                   up_proj=p + "mlp.up", down_proj=p + "mlp.down",
                                                                   act_params=p + "mlp.act")),
                           conv2=dict(channels=H, taps=cfg.canon_taps, weight=p + "canon2"))
+        else:
+            # a layer without a feed-forward reads none of the second sublayer's tensors, should a checkpoint hold them
+            unread.append(rf"l{i}\.(norm2|norm2b|canon2|mlp\..*)")
         layers.append(PartSpec("sandwich", params))
     return ModelSpec(vocab=cfg.vocab, hidden=H, embedding="embed", layers=layers, final_norm=norm("final.norm"), head="head",
-                     embed_scale=cfg.embedding_scale, logit_softcap=cfg.logit_softcap)
+                     embed_scale=cfg.embedding_scale, logit_softcap=cfg.logit_softcap, ignorable_tensors=unread)
 
 
 def tensor_shapes(cfg: PemezenConfig):

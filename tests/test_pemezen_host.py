@@ -55,6 +55,10 @@ def test_tensor_list_and_memory_plan():
     assert t["l1.mix.q"] == (3 * 16, 42) and t["l1.mix.dkv"] == (27, 42) and t["l1.mix.g"] == (27, 42) and t["l1.mix.uv"] == (27, 21)
     assert t["l2.mix.g"] == (5, 42) and t["l2.mix.o"] == (42, 65) and t["l2.mlp.act"] == (2,)
     assert "l1.norm2" not in t and "l1.canon2" not in t and "l3.mlp.up" not in t and "l3.canon1" in t
+    import re
+    unread = model.spec.ignorable_tensors       # what a checkpoint may still hold for the layers without a feed-forward
+    assert any(re.fullmatch(p, "l1.norm2b") for p in unread) and any(re.fullmatch(p, "l3.canon2") for p in unread)
+    assert not any(re.fullmatch(p, "l0.norm2") or re.fullmatch(p, "l1.norm1") for p in unread)
     # two attention layers with different row widths: a cache group each, one stream (a single vector per token)
     assert [(g.kv_heads, g.head_dim, g.planes, g.streams) for g in model.groups] == [(1, 27, 1, 1), (1, 21, 1, 1)]
     # state: per layer the mixer's (S and its convolution's inputs for a recurrent block), then the block's convolutions
