@@ -1,7 +1,8 @@
 """hymt2sharp_b200: a small, whole inference library for the Hunyuan dense
-architecture on one B200 GPU — configuration and registry, weights by name,
-layers from parts, a paged cache, one step function, a generation loop, GPU
-sampling, a command line and trace replay, on hand-written sm_100a kernels."""
+architecture and the Pemezen design on one B200 GPU — configuration and
+registry, weights by name, layers from parts, a paged cache with per-sequence
+state, one step function, a generation loop, GPU sampling, a command line and
+trace replay, on hand-written sm_100a kernels."""
 
 __version__ = "0.1.0"
 
