@@ -141,6 +141,53 @@ __global__ void rmsnorm_groups_vec_kernel(TY* __restrict__ y, const float* __res
     }
 }
 
+// Two norms around the residual sum in one pass over a row part: y (float32) += norm_a(x), then h = norm_b(y) of the new y.
+// (A sublayer's output joins the residual through a norm, and the next sublayer reads the residual through another.)
+// A thread meets the same entries in every loop, so only the two sums of squares cross threads.
+template <typename TW, typename TH>
+__global__ void rmsnorm_groups_add_norm_kernel(float* __restrict__ y, const float* __restrict__ x, const TW* __restrict__ gain_a,
+                                               TH* __restrict__ h, const TW* __restrict__ gain_b, int dim, int part, float eps_a,
+                                               float eps_b) {
+    __shared__ float scratch[33];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int r = blockIdx.x, g = blockIdx.y;
+    const size_t off = (size_t)r * dim + (size_t)g * part;
+    const float* src = x + off;
+    float* res = y + off;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < part; i += blockDim.x) ss = fmaf(src[i], src[i], ss);
+    ss = block_sum(ss, scratch);
+    const float scale_a = 1.0f / sqrtf(ss / (float)part + eps_a);
+    const TW* ga = gain_a + (size_t)g * part;
+    float ss2 = 0.f;
+    for (int i = threadIdx.x; i < part; i += blockDim.x) {
+        const float v = res[i] + src[i] * scale_a * to_float(ga[i]);
+        res[i] = v;
+        ss2 = fmaf(v, v, ss2);
+    }
+    ss2 = block_sum(ss2, scratch);
+    const float scale_b = 1.0f / sqrtf(ss2 / (float)part + eps_b);
+    const TW* gb = gain_b + (size_t)g * part;
+    TH* dst = h + off;
+    for (int i = threadIdx.x; i < part; i += blockDim.x) dst[i] = from_float<TH>(res[i] * scale_b * to_float(gb[i]));
+}
+
+HYMT2_API int hymt2_rmsnorm_groups_add_norm(float* y, const float* x, const void* gain_a, void* h, int h_dtype, const void* gain_b,
+                                            int gain_dtype, int rows, int dim, int groups, float eps_a, float eps_b,
+                                            cudaStream_t stream) {
+    if (rows == 0) return HYMT2_OK;
+    HYMT2_REQUIRE(rows > 0 && dim > 0 && groups > 0 && dim % groups == 0 && groups <= 65535,
+                  "rmsnorm: bad sizes rows=%d dim=%d groups=%d", rows, dim, groups);
+    const int part = dim / groups;
+    const int threads = part >= 1024 ? 256 : (part >= 256 ? 128 : (part >= 64 ? 64 : 32));
+    const dim3 grid(rows, groups);
+    HYMT2_DISPATCH_DTYPE(gain_dtype, TW, HYMT2_DISPATCH_DTYPE(h_dtype, TH,
+        (launch_pdl(rmsnorm_groups_add_norm_kernel<TW, TH>, grid, dim3(threads), 0, stream, y, x, (const TW*)gain_a, (TH*)h,
+                    (const TW*)gain_b, dim, part, eps_a, eps_b))));
+    return hymt2_check_launch("rmsnorm_groups_add_norm");
+}
+
 HYMT2_API int hymt2_rmsnorm_groups(void* y, int y_dtype, const void* x, int x_dtype, const void* gain, int gain_dtype,
                                    const int* rows_index, int rows, int dim, int groups, float eps, float out_scale,
                                    int add, cudaStream_t stream) {

@@ -1087,3 +1087,17 @@ def latent_attention_expanded(out: torch.Tensor, q: torch.Tensor, kexp: torch.Te
                                                   c_int(max_new_tokens), c_int(nh), c_int(dim), c_int(rot), c_int(dv), c_float(scale),
                                                   c_int(window), _stream()), "latent_attention_expanded")
 
+
+
+def rmsnorm_groups_add_norm(residual: torch.Tensor, x: torch.Tensor, gain_a: torch.Tensor, eps_a: float, out: torch.Tensor,
+                            gain_b: torch.Tensor, eps_b: float, groups: int) -> None:
+    """residual (float32) += norm_a(x); out = norm_b(residual), both norms in `groups` parts: the norm after one sublayer and the
+    norm in front of the next in one kernel."""
+    _need(residual, "residual", torch.float32, 2); _need(x, "x", torch.float32, 2); _need(out, "out", None, 2)
+    _need(gain_a, "gain_a", None, 1); _need(gain_b, "gain_b", gain_a.dtype, 1)
+    rows, dim = residual.shape
+    if x.shape != residual.shape or out.shape != residual.shape or gain_a.shape[0] != dim or gain_b.shape[0] != dim or dim % groups:
+        raise KernelError(f"rmsnorm_groups_add_norm: shapes residual {tuple(residual.shape)} x {tuple(x.shape)} out {tuple(out.shape)}")
+    _check(_lib().hymt2_rmsnorm_groups_add_norm(_ptr(residual), _ptr(x), _ptr(gain_a), _ptr(out), c_int(dtype_code(out.dtype)), _ptr(gain_b),
+                                                c_int(dtype_code(gain_a.dtype)), c_int(rows), c_int(dim), c_int(groups), c_float(eps_a),
+                                                c_float(eps_b), _stream()), "rmsnorm_groups_add_norm")

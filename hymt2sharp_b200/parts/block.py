@@ -71,8 +71,9 @@ class SandwichBlock:
 
     The convolutions run over time on each channel (parts.conv.ShortConv); their last inputs are state of the
     sequence, which this block asks the model for beside its mixer's: cache_needs() / state_bytes() have the mixer's
-    entry first, then one entry for each convolution it holds.  A sublayer's output is collected in a zeroed float32
-    buffer (mixers and feed-forwards add into what they are given) and joins the residual through the norm after it."""
+    entry first, then one entry for each convolution it holds.  A sublayer's output is collected in a float32 buffer and
+    joins the residual through the norm after it.  Mixers and feed-forwards add into what they are given, so the buffer
+    starts from zeros; a part that says `can_store = True` takes `store=True` and overwrites it instead (no zeroing)."""
 
     def __init__(self, norm1: PartSpec, mixer: PartSpec, norm1_after: PartSpec, norm2: PartSpec | None = None,
                  feed_forward: PartSpec | None = None, norm2_after: PartSpec | None = None, conv1: dict | None = None,
@@ -124,17 +125,24 @@ class SandwichBlock:
         h = self.norm1.forward(residual, ctx, ctx.dtype, fresh=True)
         if self.conv1 is not None:
             h = self.conv1.forward(h, ctx, conv_slots.pop(0))
-        branch = torch.zeros_like(residual)
-        self.mixer.forward(h, branch, ctx, slots[0])
+        if getattr(self.mixer, "can_store", False):
+            branch = torch.empty_like(residual)
+            self.mixer.forward(h, branch, ctx, slots[0], store=True)
+        else:
+            branch = torch.zeros_like(residual)
+            self.mixer.forward(h, branch, ctx, slots[0])
         ctx.prenormed = None
-        self.norm1_after.add_into(branch, residual)
         if self.feed_forward is None:
+            self.norm1_after.add_into(branch, residual)
             return
-        h = self.norm2.forward(residual, ctx, ctx.dtype, fresh=True)
+        h = self.norm1_after.add_into_then(branch, residual, self.norm2, ctx.dtype)
         if self.conv2 is not None:
             h = self.conv2.forward(h, ctx, conv_slots.pop(0))
-        branch.zero_()
-        self.feed_forward.forward(h, branch, ctx)
+        if getattr(self.feed_forward, "can_store", False):
+            self.feed_forward.forward(h, branch, ctx, store=True)
+        else:
+            branch.zero_()
+            self.feed_forward.forward(h, branch, ctx)
         ctx.prenormed = None
         self.norm2_after.add_into(branch, residual)
 

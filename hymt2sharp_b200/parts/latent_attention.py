@@ -34,6 +34,7 @@ SPLIT_KEYS_TC = 128  # the same for the tensor-core kernel, whose blocks are few
 
 class LatentAttention:
     graph_safe = True  # its forward only launches kernels on the current stream
+    can_store = True   # forward(..., store=True) overwrites `residual` with its output instead of adding to it
 
     def __init__(self, hidden: int, heads: int, dim: int, rot_dim: int, vdim: int, kv_rank: int, scale: float, eps: float,
                  position: PartSpec | None, gate: str | None, q_proj: str, dkv_proj: str, dkv_norm: str, uk_proj: str,
@@ -78,6 +79,7 @@ class LatentAttention:
             rows.append(torch.zeros((8 - total % 8, self.hidden), dtype=rows[0].dtype))
         self.proj = Linear(compute_form(torch.cat(rows, dim=0), device, dtype), role="q_dkv_gate")
         self.out = Linear(compute_form(weights[n["o"]], device, dtype), ops.EPILOGUE_ACCUMULATE, role="o_proj")
+        self.out_store = Linear(self.out.weight, ops.EPILOGUE_STORE, role="o_proj")
         # per head: W_uk[h]^T [kv_rank, dim] (the query goes into the compressed space) and W_uv[h] [vdim, kv_rank]
         uk = weights[n["uk"]].reshape(H, self.dim, self.rank).transpose(1, 2)
         self.uk_t = compute_form(uk, device, dtype)
@@ -90,7 +92,7 @@ class LatentAttention:
             self.position.load(weights, device, dtype)
 
     # -- the step ---------------------------------------------------------------
-    def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx, slot: MixerSlot) -> None:
+    def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx, slot: MixerSlot, store: bool = False) -> None:
         T, H, dl = ctx.num_tokens, self.heads, self.rank + self.rot
         rotary = self.position.kernel_epilogue(ctx) if self.position is not None else None
         if rotary is not None and rotary.rope_dim and rotary.pairing != "interleaved":
@@ -101,7 +103,7 @@ class LatentAttention:
         if (self.ukv is not None and not ctx.decode and ctx.max_new_tokens >= EXPAND_FROM_TOKENS and ctx.host_starts
                 and not any(ctx.host_starts)):
             out = self._attend_expanded(proj, rotary, plane if slot.writes else None, table, ctx)
-            self._gate_and_project(out, proj, residual, ctx)
+            self._gate_and_project(out, proj, residual, ctx, store)
             return
         q = torch.empty((T, H * dl), dtype=proj.dtype, device=proj.device)
         ops.latent_prep(proj, self.q_cols, q, plane if slot.writes else None, table, ctx.cache.block_tokens, ctx.token_seq,
@@ -118,13 +120,16 @@ class LatentAttention:
         ops.tag = "v_up"
         matmul_batched(out, mixed, self.uv, self.rank, self.vdim)
         ops.tag = None
-        self._gate_and_project(out, proj, residual, ctx)
+        self._gate_and_project(out, proj, residual, ctx, store)
 
-    def _gate_and_project(self, out, proj, residual, ctx) -> None:
+    def _gate_and_project(self, out, proj, residual, ctx, store: bool) -> None:
         if self.gate is not None:
             g0 = self.q_cols + self.rank + self.rot
             ops.sigmoid_gate(out, proj[:, g0:g0 + self.gate_cols], self.heads, self.vdim, self.gate == "head")
-        self.out.add_then_norm(out, residual, getattr(ctx, "norm_ahead", None), ctx)
+        if store:
+            self.out_store(out, out=residual)
+        else:
+            self.out.add_then_norm(out, residual, getattr(ctx, "norm_ahead", None), ctx)
 
     def _attend_expanded(self, proj, rotary, plane, table, ctx) -> torch.Tensor:
         """Whole prompts from position 0: the cache rows are written as always and also kept side by side; one product

@@ -17,6 +17,7 @@ ACTIVATIONS = ("xielu",)
 
 class DenseMLP:
     graph_safe = True
+    can_store = True   # forward(..., store=True) overwrites `residual` with its output instead of adding to it
 
     def __init__(self, hidden: int, intermediate: int, activation: str, up_proj: str, down_proj: str, act_params: str | None = None):
         if activation not in ACTIVATIONS:
@@ -34,15 +35,19 @@ class DenseMLP:
         n = self.names
         self.up = Linear(compute_form(weights[n["u"]], device, dtype), role="up")
         self.down = Linear(compute_form(weights[n["d"]], device, dtype), ops.EPILOGUE_ACCUMULATE, role="down")
+        self.down_store = Linear(self.down.weight, ops.EPILOGUE_STORE, role="down")
         self.pq = weights[n["a"]].to(device).float().contiguous()
 
     def first_weights(self):
         return self.up.weight if self.up is not None else None
 
-    def forward(self, x, residual: torch.Tensor, ctx) -> None:
+    def forward(self, x, residual: torch.Tensor, ctx, store: bool = False) -> None:
         z = self.up(x, ctx=ctx)
         ops.xielu(z, z, self.pq)
-        self.down.add_then_norm(z, residual, getattr(ctx, "norm_ahead", None), ctx)
+        if store:
+            self.down_store(z, out=residual)
+        else:
+            self.down.add_then_norm(z, residual, getattr(ctx, "norm_ahead", None), ctx)
 
 
 register_part("feed_forward", "dense_mlp", DenseMLP)

@@ -51,5 +51,16 @@ class RMSNorm:
         """residual (float32) += norm(x): a sublayer's output that is normed before it joins the residual stream."""
         ops.rmsnorm_groups(residual, x, self.gain, self.eps, self.groups, add=True)
 
+    def add_into_then(self, x: torch.Tensor, residual: torch.Tensor, following: "RMSNorm", out_dtype: torch.dtype) -> torch.Tensor:
+        """add_into, and what `following` (the norm that reads the residual next) makes of the new rows: one kernel where
+        the two norms cut their rows alike, two otherwise."""
+        if (following.dim, following.groups) == (self.dim, self.groups) and following.gain.dtype == self.gain.dtype \
+                and x.dtype == torch.float32 and x.shape == residual.shape:
+            out = torch.empty(residual.shape, dtype=out_dtype, device=residual.device)
+            ops.rmsnorm_groups_add_norm(residual, x, self.gain, self.eps, out, following.gain, following.eps, self.groups)
+            return out
+        self.add_into(x, residual)
+        return following.forward(residual, None, out_dtype, fresh=True)
+
 
 register_part("norm", "rmsnorm", RMSNorm)

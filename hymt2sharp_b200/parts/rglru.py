@@ -23,6 +23,7 @@ from .linear import Linear, compute_form, matmul_batched
 
 class RGLRU:
     graph_safe = True
+    can_store = True   # forward(..., store=True) overwrites `residual` with its output instead of adding to it
 
     def __init__(self, hidden: int, width: int, blocks: int, taps: int, decay: float, y_proj: str, y_bias: str, x_proj: str,
                  x_bias: str, conv: str, conv_bias: str, r_gate: str, r_bias: str, i_gate: str, i_bias: str, lam: str,
@@ -58,9 +59,10 @@ class RGLRU:
         self.ra, self.ia = compute_form(weights[n["ra"]], device, dtype), compute_form(weights[n["ia"]], device, dtype)
         self.rb, self.ib, self.lam = small(n["rb"]), small(n["ib"]), small(n["lam"])
         self.out = Linear(compute_form(weights[n["o"]], device, dtype), ops.EPILOGUE_ACCUMULATE, role="o_proj")
+        self.out_store = Linear(self.out.weight, ops.EPILOGUE_STORE, role="o_proj")
         self.conv.load(weights, device, dtype)
 
-    def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx, slot: MixerSlot) -> None:
+    def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx, slot: MixerSlot, store: bool = False) -> None:
         T, W, B = ctx.num_tokens, self.width, self.blocks
         bw = W // B
         yx = self.yx(x, ctx=ctx)                        # [T, y | x] before their biases
@@ -75,7 +77,10 @@ class RGLRU:
         mixed = torch.empty((T, W), dtype=u.dtype, device=u.device)
         ops.rglru_scan(mixed, gates, u, yx[:, :W], self.rb, self.ib, self.lam, self.decay, ctx.cache.state, slot.state_offset,
                        ctx.cu_seqlens, ctx.slot_ids, ctx.kv_lens, ctx.num_seqs, ctx.max_new_tokens)
-        self.out.add_then_norm(mixed, residual, getattr(ctx, "norm_ahead", None), ctx)
+        if store:
+            self.out_store(mixed, out=residual)
+        else:
+            self.out.add_then_norm(mixed, residual, getattr(ctx, "norm_ahead", None), ctx)
 
 
 register_part("mixer", "rglru", RGLRU)
