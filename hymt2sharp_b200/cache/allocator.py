@@ -31,9 +31,14 @@ class GroupSpec:
     window: int = 0         # for kind "window": positions that stay visible
     streams: int = 2        # tensors per plane: 2 = keys and values; 1 = one vector per token that serves as both
                             # (a compressed key/value row: kv_heads 1, head_dim its width)
+    value_dim: int = 0      # entries of a value row where they differ from a key row's head_dim (0: the same)
 
     def key(self):
-        return (self.kind, self.kv_heads, self.head_dim, self.window, self.streams)
+        return (self.kind, self.kv_heads, self.head_dim, self.window, self.streams, self.value_width)
+
+    @property
+    def value_width(self) -> int:
+        return self.value_dim or self.head_dim
 
 
 class FreeList:

@@ -3,7 +3,9 @@ layers, the block tables that kernels read, and the fixed-size state area.
 
 Storage of one group: [plane, stream (keys, values; or the one vector of a group
 with a single stream), block, kv head, token in block, head_dim]; a plane is one
-layer's share.  `tables[g]` is an int32 device matrix
+layer's share.  A group whose value rows are of another width than its key rows
+has one flat tensor instead: all planes' keys [plane, block, kv head, token in
+block, head_dim], then all planes' values [.., value_dim].  `tables[g]` is an int32 device matrix
 [slot, logical block] → physical block (-1: none).  The host copy of the tables
 is the truth; rows that changed are sent before a step runs.
 
@@ -32,8 +34,14 @@ class PagedCache:
         self.num_blocks = -(-capacity_tokens // block_tokens)
         max_slots = max(1, min(max_slots, self.num_blocks))
         self.book = CacheBook(self.groups, self.num_blocks, block_tokens, max_slots)
-        self.storage = [torch.zeros((g.planes, g.streams, self.num_blocks, g.kv_heads, block_tokens, g.head_dim),
-                                    dtype=dtype, device=self.device) for g in self.groups]
+        self.storage = []
+        for g in self.groups:
+            if g.streams == 2 and g.value_width != g.head_dim:
+                rows = g.planes * self.num_blocks * g.kv_heads * block_tokens
+                self.storage.append(torch.zeros(rows * (g.head_dim + g.value_width), dtype=dtype, device=self.device))
+            else:
+                self.storage.append(torch.zeros((g.planes, g.streams, self.num_blocks, g.kv_heads, block_tokens, g.head_dim),
+                                                dtype=dtype, device=self.device))
         cols = self.num_blocks if max_sequence_tokens is None else -(-max_sequence_tokens // block_tokens)
         self.table_cols = max(1, min(cols, self.num_blocks))
         if max_sequence_tokens is None:
@@ -55,11 +63,15 @@ class PagedCache:
 
     def bytes_per_token(self) -> int:
         es = torch.empty((), dtype=self.dtype).element_size()
-        return sum(g.streams * g.planes * g.kv_heads * g.head_dim * es for g in self.groups)
+        return sum(g.planes * g.kv_heads * (g.head_dim + (g.value_width if g.streams > 1 else 0)) * es for g in self.groups)
 
     def plane(self, group: int, plane: int) -> tuple[torch.Tensor, torch.Tensor | None]:
         """(keys, values) of a plane; a group with one stream has (vectors, None)."""
-        s = self.storage[group]
+        s, g = self.storage[group], self.groups[group]
+        if s.dim() == 1:
+            shape = (g.planes, self.num_blocks, g.kv_heads, self.block_tokens)
+            rows = g.planes * self.num_blocks * g.kv_heads * self.block_tokens
+            return (s[: rows * g.head_dim].view(*shape, g.head_dim)[plane], s[rows * g.head_dim:].view(*shape, g.value_width)[plane])
         return s[plane, 0], (s[plane, 1] if s.shape[1] > 1 else None)
 
     # -- growth -----------------------------------------------------------------

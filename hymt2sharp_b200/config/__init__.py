@@ -1,8 +1,9 @@
 from .base import ConfigError, ConfigReader, read_config_json, architecture_name
 from .hunyuan_dense import HunyuanDenseConfig
 from .pemezen import PemezenConfig
+from .novunex import NovunexConfig
 from .registry import (Architecture, register_architecture, get_architecture,
                        known_architectures, load_config)
 
-__all__ = ["ConfigError", "ConfigReader", "read_config_json", "architecture_name", "HunyuanDenseConfig", "PemezenConfig",
+__all__ = ["ConfigError", "ConfigReader", "read_config_json", "architecture_name", "HunyuanDenseConfig", "PemezenConfig", "NovunexConfig",
            "Architecture", "register_architecture", "get_architecture", "known_architectures", "load_config"]

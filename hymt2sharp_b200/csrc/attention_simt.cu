@@ -39,6 +39,7 @@ struct AttnParams {
     int v_from_k;           // the values are the first dv entries of the key rows (one vector per token serves as both)
     float scale;
     int* status;            // may be null; [0] = 2 when a row is longer than max_splits * split_keys covers
+    int sink;               // the softmax has one more term in its denominator, of score 0 and without a value
 };
 
 template <typename T, int NACC>
@@ -178,7 +179,14 @@ attention_simt_kernel(AttnParams p) {
             ml[1] = l;
         }
     } else {
-        const float inv = l > 0.f ? 1.0f / l : 0.f;
+        // with a sink: p_j = exp(s_j - M) / (exp(-M) + sum_j exp(s_j - M)) with M = max(m, 0), so that neither term overflows
+        float up = 1.f;
+        if (p.sink) {
+            const float M = fmaxf(m, 0.f);
+            up = expf(m - M);
+            l = l * up + expf(-M);
+        }
+        const float inv = l > 0.f ? up / l : 0.f;
         T* o = (T*)p.out + row_index * dv;
 #pragma unroll
         for (int i = 0; i < NACC; i++) {
@@ -213,9 +221,9 @@ __global__ void attention_merge_kernel(AttnParams p, int total_tokens) {
         return;
     }
     const float* ml = p.part_ml + (size_t)row * p.max_splits * 2;
-    float M = -INFINITY;
+    float M = p.sink ? 0.f : -INFINITY;   // the sink is one more partial with maximum 0 and sum 1
     for (int s = s_begin; s < s_end; s++) M = fmaxf(M, ml[2 * s]);
-    float L = 0.f;
+    float L = p.sink ? expf(-M) : 0.f;
     for (int s = s_begin; s < s_end; s++) L += ml[2 * s + 1] * expf(ml[2 * s] - M);
     const float inv = L > 0.f ? 1.0f / L : 0.f;
     const float* pa = p.part_acc + (size_t)row * p.max_splits * p.dv;
@@ -286,7 +294,7 @@ static int attention_simt_general(void* out, const void* q, const void* k_cache,
                                   const int* cu_seqlens, const int* slot_ids, const int* kv_lens,
                                   int batch, int tokens, int max_new_tokens, int nh, int nkv, int d, int dv,
                                   float scale, int window, int split_keys, int max_splits,
-                                  float* part_acc, float* part_ml, cudaStream_t stream, int* status) {
+                                  float* part_acc, float* part_ml, cudaStream_t stream, int* status, int sink = 0) {
     if (tokens == 0 || batch == 0) return HYMT2_OK;
     HYMT2_REQUIRE(batch > 0 && tokens > 0 && nh > 0 && nkv > 0, "attention: bad sizes");
     HYMT2_REQUIRE(nh % nkv == 0, "attention: %d heads are not a multiple of %d kv heads", nh, nkv);
@@ -310,6 +318,7 @@ static int attention_simt_general(void* out, const void* q, const void* k_cache,
     p.split_keys = split_keys; p.max_splits = split_keys > 0 ? max_splits : 1;
     p.scale = scale;
     p.status = status;
+    p.sink = sink;
     const size_t smem = sizeof(float) * ((size_t)ROWS * d + (size_t)KEY_TILE * (d + 1) + (v_cache ? (size_t)KEY_TILE * dv : 0) + ROWS * KEY_TILE);
     dim3 grid((max_new_tokens + p.tokens_per_tile - 1) / p.tokens_per_tile, nkv * p.head_chunks, batch * p.max_splits);
     HYMT2_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "attention: grid too large (batch %d x splits %d)", batch, p.max_splits);
@@ -341,6 +350,19 @@ HYMT2_API int hymt2_attention_simt(void* out, const void* q, const void* k_cache
     return attention_simt_general(out, q, k_cache, v_cache, dtype, block_table, table_stride, block_tokens, cu_seqlens, slot_ids,
                                   kv_lens, batch, tokens, max_new_tokens, nh, nkv, d, d, scale, window, split_keys, max_splits,
                                   part_acc, part_ml, stream, status);
+}
+
+// Keys of d and values of dv entries a head, each in a plane of its own, and optionally a sink in the softmax.
+HYMT2_API int hymt2_attention_simt_kv(void* out, const void* q, const void* k_cache, const void* v_cache, int dtype,
+                                      const int* block_table, int table_stride, int block_tokens,
+                                      const int* cu_seqlens, const int* slot_ids, const int* kv_lens,
+                                      int batch, int tokens, int max_new_tokens, int nh, int nkv, int d, int dv,
+                                      float scale, int window, int sink, int split_keys, int max_splits,
+                                      float* part_acc, float* part_ml, cudaStream_t stream, int* status) {
+    HYMT2_REQUIRE(v_cache != nullptr, "attention: no values");
+    return attention_simt_general(out, q, k_cache, v_cache, dtype, block_table, table_stride, block_tokens, cu_seqlens, slot_ids,
+                                  kv_lens, batch, tokens, max_new_tokens, nh, nkv, d, dv, scale, window, split_keys, max_splits,
+                                  part_acc, part_ml, stream, status, sink);
 }
 
 // Attention over a cache that holds ONE vector per token and layer, shared by all heads: the key of every head

@@ -70,6 +70,31 @@ __global__ void xielu_kernel(T* __restrict__ out, const T* __restrict__ x, const
     store_pack<T, V>(out + i, pk);
 }
 
+// The square of relu: max(z, 0)^2.
+template <typename T, int V>
+__global__ void relu_squared_kernel(T* __restrict__ out, const T* __restrict__ x, size_t total) {
+    pdl_wait();   // everything in front is complete before anything is read; then the next kernel may be set up meanwhile
+    pdl_launch_dependents();
+    const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * V;
+    if (i >= total) return;
+    Pack<T, V> pk = load_pack<T, V>(x + i);
+#pragma unroll
+    for (int k = 0; k < V; k++) {
+        const float z = fmaxf(to_float(pk.v[k]), 0.f);
+        pk.v[k] = from_float<T>(z * z);
+    }
+    store_pack<T, V>(out + i, pk);
+}
+
+// out = x rounded to out's type
+template <typename TO, typename TI>
+__global__ void convert_kernel(TO* __restrict__ out, const TI* __restrict__ x, size_t total) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < total) out[i] = from_float<TO>(to_float(x[i]));
+}
+
 // x[t, h, v] <- x[t, h, v] * sigmoid(g[t, per_head ? h : h * vdim + v])
 template <typename T, int V>
 __global__ void sigmoid_gate_kernel(T* __restrict__ x, const T* __restrict__ g, int heads, int vdim, long ldg, int per_head,
@@ -131,6 +156,27 @@ HYMT2_API int hymt2_xielu(void* out, const void* x, int dtype, const float* pq, 
             launch_pdl(xielu_kernel<T, 1>, dim3(blocks_for((size_t)total)), dim3(256), 0, stream, (T*)out, (const T*)x, pq, (size_t)total);
     });
     return hymt2_check_launch("xielu");
+}
+
+HYMT2_API int hymt2_relu_squared(void* out, const void* x, int dtype, long total, cudaStream_t stream) {
+    if (total == 0) return HYMT2_OK;
+    HYMT2_REQUIRE(total > 0, "relu_squared: bad sizes");
+    HYMT2_DISPATCH_DTYPE(dtype, T, {
+        constexpr int V = 16 / sizeof(T);
+        if (total % V == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)out % 16 == 0)
+            launch_pdl(relu_squared_kernel<T, V>, dim3(blocks_for((size_t)total / V)), dim3(256), 0, stream, (T*)out, (const T*)x, (size_t)total);
+        else
+            launch_pdl(relu_squared_kernel<T, 1>, dim3(blocks_for((size_t)total)), dim3(256), 0, stream, (T*)out, (const T*)x, (size_t)total);
+    });
+    return hymt2_check_launch("relu_squared");
+}
+
+HYMT2_API int hymt2_convert(void* out, int out_dtype, const void* x, int x_dtype, long total, cudaStream_t stream) {
+    if (total == 0) return HYMT2_OK;
+    HYMT2_REQUIRE(total > 0, "convert: bad sizes");
+    HYMT2_DISPATCH_DTYPE(out_dtype, TO, HYMT2_DISPATCH_DTYPE(x_dtype, TI,
+        (launch_pdl(convert_kernel<TO, TI>, dim3(blocks_for((size_t)total)), dim3(256), 0, stream, (TO*)out, (const TI*)x, (size_t)total))));
+    return hymt2_check_launch("convert");
 }
 
 HYMT2_API int hymt2_sigmoid_gate(void* x, const void* g, int dtype, int rows, int heads, int vdim, long ldg, int per_head,

@@ -135,6 +135,79 @@ int launch(void* C, const void* A, const void* W, int M, int N, int K, long lda,
 }
 
 
+// A grouped product: the rows of A are sorted by the matrix they meet (an expert of a mixture), in segments padded to whole
+// tiles of BM rows.  `tile_group[i]` names the matrix of row tile i (-1: the tile is not in use), `row_source[r]` the row of
+// A that sorted row r reads (-1: a padding row; with `gather` 0 it only says which rows are in use, and sorted row r reads
+// row r of A).  C has one row per sorted row.  Epilogues: 0 store,
+// 3 the square of relu.  Sums run in ascending K as everywhere, so a row's result depends on nothing but the row.
+enum { EPI_RELU_SQUARED = 3 };
+
+template <typename TA, typename TW, typename TC, int EPI>
+__global__ void __launch_bounds__(THREADS)
+gemm_simt_grouped_kernel(TC* __restrict__ C, const TA* __restrict__ A, const TW* __restrict__ W, const int* __restrict__ tile_group,
+                         const int* __restrict__ row_source, int gather, int N, int K, long lda, long ldc, long w_gs, bool vec_a,
+                         bool vec_w) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int group = tile_group[blockIdx.y];
+    if (group < 0) return;
+    W += (size_t)group * w_gs;
+    __shared__ float As[BK][BM + 4];
+    __shared__ float Ws[BK][BN + 4];
+    __shared__ int rows_ok[BM];
+    const int tid = threadIdx.x;
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int lrow = tid >> 2, lk = (tid & 3) * 4;
+    const int tm = (tid >> 4) * TM, tn = (tid & 15) * TN;
+    float acc[TM][TN];
+#pragma unroll
+    for (int i = 0; i < TM; i++)
+#pragma unroll
+        for (int j = 0; j < TN; j++) acc[i][j] = 0.f;
+    int src_row = row_source ? row_source[m0 + lrow] : m0 + lrow;
+    if ((tid & 3) == 0) rows_ok[lrow] = src_row >= 0;
+    if (!gather && src_row >= 0) src_row = m0 + lrow;
+    const bool a_ok = src_row >= 0, w_ok = n0 + lrow < N;
+    const TA* a_row = A + (size_t)(a_ok ? src_row : 0) * lda;
+    const TW* w_row = W + (size_t)(w_ok ? n0 + lrow : 0) * K;
+    for (int k0 = 0; k0 < K; k0 += BK) {
+        float va[4], vw[4];
+        load4(a_row, k0 + lk, K, a_ok, vec_a, va);
+        load4(w_row, k0 + lk, K, w_ok, vec_w, vw);
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            As[lk + i][lrow] = va[i];
+            Ws[lk + i][lrow] = vw[i];
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < BK; kk++) {
+            float a[TM], w[TN];
+#pragma unroll
+            for (int i = 0; i < TM; i++) a[i] = As[kk][tm + i];
+#pragma unroll
+            for (int j = 0; j < TN; j++) w[j] = Ws[kk][tn + j];
+#pragma unroll
+            for (int i = 0; i < TM; i++)
+#pragma unroll
+                for (int j = 0; j < TN; j++) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < TM; i++) {
+        if (!rows_ok[tm + i]) continue;
+#pragma unroll
+        for (int j = 0; j < TN; j++) {
+            const int n = n0 + tn + j;
+            if (n >= N) continue;
+            float v = acc[i][j];
+            if constexpr (EPI == EPI_RELU_SQUARED) { v = fmaxf(v, 0.f); v = v * v; }
+            C[(size_t)(m0 + tm + i) * ldc + n] = from_float<TC>(v);
+        }
+    }
+}
+
 // Few rows (a decode step's tokens) against a batch of small matrices: one warp per output column reads its weight
 // row once, 16 bytes a lane, and keeps a float32 sum for every row of A; the sums of a row do not depend on how many
 // other rows there are.  The time is that of reading W once.
@@ -237,3 +310,28 @@ HYMT2_API int hymt2_gemm_skinny_batched(void* C, int c_dtype, const void* A, con
     });
     return hymt2_check_launch("gemm_skinny_batched");
 }
+
+// The grouped product (see gemm_simt_grouped_kernel): `tiles` row tiles of 64 sorted rows, W holds the groups' matrices
+// [N, K] one after the other (w_gs elements apart).
+HYMT2_API int hymt2_gemm_simt_grouped(void* C, int c_dtype, const void* A, int a_dtype, const void* W, int w_dtype,
+                                      const int* tile_group, const int* row_source, int gather, int tiles, int N, int K, long lda, long ldc,
+                                      long w_gs, int epilogue, cudaStream_t stream) {
+    if (tiles == 0 || N == 0) return HYMT2_OK;
+    HYMT2_REQUIRE(tiles > 0 && tiles <= 65535 && N > 0 && K > 0, "gemm_grouped: bad sizes tiles=%d N=%d K=%d", tiles, N, K);
+    HYMT2_REQUIRE(epilogue == EPI_STORE || epilogue == EPI_RELU_SQUARED, "gemm_grouped: unknown epilogue %d", epilogue);
+    HYMT2_REQUIRE(lda >= K && ldc >= N && tile_group, "gemm_grouped: bad arguments");
+    const dim3 grid((N + BN - 1) / BN, tiles);
+    HYMT2_DISPATCH_DTYPE(a_dtype, TA, HYMT2_DISPATCH_DTYPE(w_dtype, TW, HYMT2_DISPATCH_DTYPE(c_dtype, TC, {
+        const bool vec_a = (lda % 4 == 0) && ((uintptr_t)A % 16 == 0);
+        const bool vec_w = (K % 4 == 0) && ((uintptr_t)W % 16 == 0) && (w_gs * sizeof(TW)) % 16 == 0;
+        if (epilogue == EPI_STORE)
+            launch_pdl(gemm_simt_grouped_kernel<TA, TW, TC, EPI_STORE>, grid, dim3(THREADS), 0, stream, (TC*)C, (const TA*)A, (const TW*)W,
+                       tile_group, row_source, gather, N, K, lda, ldc, w_gs, vec_a, vec_w);
+        else
+            launch_pdl(gemm_simt_grouped_kernel<TA, TW, TC, EPI_RELU_SQUARED>, grid, dim3(THREADS), 0, stream, (TC*)C, (const TA*)A,
+                       (const TW*)W, tile_group, row_source, gather, N, K, lda, ldc, w_gs, vec_a, vec_w);
+    })));
+    return hymt2_check_launch("gemm_simt_grouped");
+}
+
+HYMT2_API int hymt2_gemm_simt_group_tile() { return BM; }

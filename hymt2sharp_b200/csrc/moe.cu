@@ -1,0 +1,185 @@
+// Routing of a mixture of experts: from the router's outputs to the chosen experts and their weights, from there to
+// the rows sorted by expert that the grouped products read, and from the experts' outputs back to one row per token.
+// Everything here is float32 and integer arithmetic; nothing depends on the order in which blocks run (no atomics), so a
+// token's result does not depend on what else is in the step.
+//
+//   route    scores s = softmax(z) over ALL router outputs; the `top` largest of s + correction are chosen (ties: the
+//            lower index); a chosen output's weight is its s, without the correction and not renormalised
+//   count    how many (token, choice) pairs name each expert that has tensors (outputs from `experts` on name identity
+//            experts, which need no product)
+//   place    every expert's pairs, in token order, get consecutive rows of a sorted list; an expert's segment is padded to
+//            whole tiles of `tile` rows.  Written: pair_row[pair] (-1 for identity experts), row_token[row] (-1 for padding),
+//            tile_group[tile] (-1 for tiles not in use)
+//   combine  out[t] = sum over the token's choices, in the order they were chosen, of weight * (the expert's output row, or
+//            the token's own input row for an identity expert)
+#include "common.cuh"
+
+namespace {
+
+constexpr int ROUTE_WARPS = 4;
+
+__global__ void __launch_bounds__(ROUTE_WARPS * 32)
+moe_route_kernel(int* __restrict__ chosen, float* __restrict__ weight, const float* __restrict__ logits,
+                 const float* __restrict__ correction, int tokens, int outputs, int top) {
+    extern __shared__ float smem[];   // [ROUTE_WARPS][2 * outputs]: scores, choice scores
+    pdl_wait();
+    pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * ROUTE_WARPS + warp;
+    if (t >= tokens) return;
+    float* s = smem + (size_t)warp * 2 * outputs;
+    float* c = s + outputs;
+    const float* z = logits + (size_t)t * outputs;
+    float m = -INFINITY;
+    for (int i = lane; i < outputs; i += 32) m = fmaxf(m, z[i]);
+    m = warp_max(m);
+    float sum = 0.f;
+    for (int i = lane; i < outputs; i += 32) { const float e = expf(z[i] - m); s[i] = e; sum += e; }
+    sum = warp_sum(sum);
+    const float inv = 1.0f / sum;
+    for (int i = lane; i < outputs; i += 32) {
+        s[i] *= inv;
+        c[i] = s[i] + (correction ? correction[i] : 0.f);
+    }
+    __syncwarp();
+    for (int k = 0; k < top; k++) {
+        float best = -INFINITY;
+        int at = 0x7fffffff;
+        for (int i = lane; i < outputs; i += 32)
+            if (c[i] > best) { best = c[i]; at = i; }   // ascending i: the first of equals stays
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+            if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+        }
+        if (lane == 0) {
+            chosen[(size_t)t * top + k] = at;
+            weight[(size_t)t * top + k] = s[at];
+            c[at] = -INFINITY;
+        }
+        __syncwarp();
+    }
+}
+
+constexpr int PLACE_THREADS = 256;
+
+__global__ void __launch_bounds__(PLACE_THREADS)
+moe_count_kernel(int* __restrict__ counts, const int* __restrict__ chosen, int pairs, int experts) {
+    __shared__ float scratch[33];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int e = blockIdx.x;
+    int n = 0;
+    if (e < experts)   // (a mixture of identity experts only still runs one block, which finds nothing)
+        for (int i = threadIdx.x; i < pairs; i += blockDim.x) n += chosen[i] == e;
+    // (counts of up to 2^24 are exact in float32)
+    const float total = block_sum((float)n, scratch);
+    if (threadIdx.x == 0) counts[e] = (int)total;
+}
+
+__global__ void __launch_bounds__(PLACE_THREADS)
+moe_place_kernel(int* __restrict__ pair_row, int* __restrict__ row_token, int* __restrict__ tile_group,
+                 const int* __restrict__ counts, const int* __restrict__ chosen, int pairs, int top, int experts, int tile,
+                 int max_tiles) {
+    __shared__ int warp_total[PLACE_THREADS / 32];
+    __shared__ int base_s, running_s;
+    pdl_wait();
+    pdl_launch_dependents();
+    const int e = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) {
+        int rows = 0;
+        for (int i = 0; i < e; i++) rows += (counts[i] + tile - 1) / tile * tile;
+        base_s = rows;
+        running_s = 0;
+    }
+    __syncthreads();
+    const int base = base_s;
+    const int mine = counts[e];
+    for (int i0 = 0; i0 < pairs; i0 += PLACE_THREADS) {
+        const int i = i0 + threadIdx.x;
+        const int c = i < pairs ? chosen[i] : -1;
+        const bool hit = c == e && e < experts;
+        if (e == 0 && c >= experts) pair_row[i] = -1;
+        const unsigned ballot = __ballot_sync(0xffffffffu, hit);
+        if (lane == 0) warp_total[warp] = __popc(ballot);
+        __syncthreads();
+        int before = running_s;
+        for (int w = 0; w < warp; w++) before += warp_total[w];
+        if (hit) {
+            const int row = base + before + __popc(ballot & ((1u << lane) - 1u));
+            pair_row[i] = row;
+            row_token[row] = i / top;
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int all = 0;
+            for (int w = 0; w < PLACE_THREADS / 32; w++) all += warp_total[w];
+            running_s += all;
+        }
+        __syncthreads();
+    }
+    const int padded = (mine + tile - 1) / tile * tile;
+    for (int r = mine + threadIdx.x; r < padded; r += blockDim.x) row_token[base + r] = -1;
+    for (int i = threadIdx.x; i < padded / tile; i += blockDim.x) tile_group[base / tile + i] = e;
+    if (e == (int)gridDim.x - 1)
+        for (int i = (base + padded) / tile + threadIdx.x; i < max_tiles; i += blockDim.x) tile_group[i] = -1;
+}
+
+// one block per token
+template <typename TX>
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(float* __restrict__ out, const float* __restrict__ y, const TX* __restrict__ x, const int* __restrict__ pair_row,
+                   const float* __restrict__ weight, int width, int top, int add) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t t = blockIdx.x;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float acc = add ? out[t * width + i] : 0.f;
+        for (int k = 0; k < top; k++) {
+            const int row = pair_row[t * top + k];
+            const float v = row >= 0 ? y[(size_t)row * width + i] : to_float(x[t * width + i]);
+            acc = fmaf(weight[t * top + k], v, acc);
+        }
+        out[t * width + i] = acc;
+    }
+}
+
+}  // namespace
+
+HYMT2_API int hymt2_moe_route(int* chosen, float* weight, const float* logits, const float* correction, int tokens, int outputs,
+                              int top, cudaStream_t stream) {
+    if (tokens == 0) return HYMT2_OK;
+    HYMT2_REQUIRE(tokens > 0 && outputs > 0 && top > 0 && top <= outputs, "moe_route: bad sizes tokens=%d outputs=%d top=%d", tokens, outputs, top);
+    const size_t smem = (size_t)ROUTE_WARPS * 2 * outputs * sizeof(float);
+    HYMT2_REQUIRE(smem <= 48 * 1024, "moe_route: %d router outputs are too many", outputs);
+    launch_pdl(moe_route_kernel, dim3((tokens + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(ROUTE_WARPS * 32), smem, stream, chosen, weight,
+               logits, correction, tokens, outputs, top);
+    return hymt2_check_launch("moe_route");
+}
+
+// counts [experts] is scratch; row_token holds pairs + experts * (tile - 1) rows rounded up to whole tiles, tile_group one entry
+// for each of those tiles (max_tiles).
+HYMT2_API int hymt2_moe_place(int* pair_row, int* row_token, int* tile_group, int* counts, const int* chosen, int tokens, int top,
+                              int experts, int tile, int max_tiles, cudaStream_t stream) {
+    if (tokens == 0) return HYMT2_OK;
+    HYMT2_REQUIRE(tokens > 0 && top > 0 && experts >= 0 && tile > 0, "moe_place: bad sizes");
+    HYMT2_REQUIRE((long)tokens * top < (1L << 24), "moe_place: too many (token, choice) pairs");
+    HYMT2_REQUIRE((long)max_tiles * tile >= (long)tokens * top + (long)experts * (tile - 1), "moe_place: too few tiles");
+    const int pairs = tokens * top;
+    const int blocks = experts > 0 ? experts : 1;
+    launch_pdl(moe_count_kernel, dim3(blocks), dim3(PLACE_THREADS), 0, stream, counts, chosen, pairs, experts);
+    launch_pdl(moe_place_kernel, dim3(blocks), dim3(PLACE_THREADS), 0, stream, pair_row, row_token, tile_group, (const int*)counts, chosen,
+               pairs, top, experts, tile, max_tiles);
+    return hymt2_check_launch("moe_place");
+}
+
+HYMT2_API int hymt2_moe_combine(float* out, const float* y, const void* x, int x_dtype, const int* pair_row, const float* weight,
+                                int tokens, int width, int top, int add, cudaStream_t stream) {
+    if (tokens == 0) return HYMT2_OK;
+    HYMT2_REQUIRE(tokens > 0 && width > 0 && top > 0, "moe_combine: bad sizes");
+    HYMT2_DISPATCH_DTYPE(x_dtype, TX, (launch_pdl(moe_combine_kernel<TX>, dim3(tokens), dim3(256), 0, stream, out, y, (const TX*)x, pair_row,
+                                                  weight, width, top, add)));
+    return hymt2_check_launch("moe_combine");
+}

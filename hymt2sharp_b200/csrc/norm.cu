@@ -141,7 +141,8 @@ __global__ void rmsnorm_groups_vec_kernel(TY* __restrict__ y, const float* __res
     }
 }
 
-// Two norms around the residual sum in one pass over a row part: y (float32) += norm_a(x), then h = norm_b(y) of the new y.
+// Two norms around the residual sum in one pass over a row part: y (float32) += norm_a(x), then h = norm_b(y) of the new y
+// (gain_b null: h = the new y itself, rounded to h's type).
 // (A sublayer's output joins the residual through a norm, and the next sublayer reads the residual through another.)
 // A thread meets the same entries in every loop, so only the two sums of squares cross threads.
 template <typename TW, typename TH>
@@ -166,10 +167,14 @@ __global__ void rmsnorm_groups_add_norm_kernel(float* __restrict__ y, const floa
         res[i] = v;
         ss2 = fmaf(v, v, ss2);
     }
+    TH* dst = h + off;
+    if (gain_b == nullptr) {   // no second norm: the next sublayer reads the new rows as they are, in its own type
+        for (int i = threadIdx.x; i < part; i += blockDim.x) dst[i] = from_float<TH>(res[i]);
+        return;
+    }
     ss2 = block_sum(ss2, scratch);
     const float scale_b = 1.0f / sqrtf(ss2 / (float)part + eps_b);
     const TW* gb = gain_b + (size_t)g * part;
-    TH* dst = h + off;
     for (int i = threadIdx.x; i < part; i += blockDim.x) dst[i] = from_float<TH>(res[i] * scale_b * to_float(gb[i]));
 }
 

@@ -9,8 +9,14 @@
 // tensor and k, v go to the cache row of (slot, position)
 // (src/HyMT2Sharp/HunyuanDenseModel.Prefill.cs:60-61).  All arithmetic is float32.
 //
+// The general kernel knows more forms.  Values may be narrower or wider than keys (dv entries a head).  The
+// norm of q and k may come BEFORE the rotation, per head with a gain of d entries (norm_mode 2) or over a token's
+// whole projection at once, all heads together, with a gain as wide as the projection (norm_mode 3); mode 1 is
+// the per-head norm after the rotation, mode 0 none.  And the input may hold queries only (has_kv 0: a layer
+// that reads another layer's keys and values).
+//
 // Cache layout of one plane (one layer's keys or values):
-//   [block][kv head][token in block][d]
+//   [block][kv head][token in block][d]   (values: [dv])
 // `block_table[slot * table_stride + pos / block_tokens]` names the block.
 // A token whose batch row has slot < 0 is padding: its q is written, its k and v
 // are dropped.
@@ -34,7 +40,10 @@ struct RopeKvParams {
     const void* k_gain;     // [d] or null
     int table_stride, block_tokens, nh, nkv, d, rope_dim, write_kv;
     float eps;
+    int dv, norm_mode, has_kv;
 };
+
+enum { NORM_NONE = 0, NORM_HEAD_AFTER = 1, NORM_HEAD_BEFORE = 2, NORM_ALL_BEFORE = 3 };
 
 template <typename T, typename TG>
 __global__ void __launch_bounds__(128)
@@ -46,32 +55,53 @@ rope_kv_kernel(RopeKvParams p, int tokens) {
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float* row = smem + warp * p.d;
-    const int total_heads = p.nh + 2 * p.nkv;
+    const int total_heads = p.nh + (p.has_kv ? 2 * p.nkv : 0);
     // one warp per (token, head)
     const long item = (long)blockIdx.x * 4 + warp;
     if (item >= (long)tokens * total_heads) return;
     const int t = (int)(item / total_heads), head = (int)(item % total_heads);
-    const int d = p.d, half = p.rope_dim / 2;
+    const int d = p.d, dv = p.dv, half = p.rope_dim / 2;
     const int pos = p.token_pos[t];
     const int slot = p.slot_ids[p.token_seq[t]];
     const bool is_q = head < p.nh, is_k = !is_q && head < p.nh + p.nkv;
     const bool write_kv = p.write_kv && slot >= 0;
     if (!is_q && !write_kv) return;
-    const T* src = (const T*)p.qkv + ((size_t)t * total_heads + head) * d;
+    const size_t in_row = (size_t)p.nh * d + (p.has_kv ? (size_t)p.nkv * (d + dv) : 0);
+    const T* tok = (const T*)p.qkv + (size_t)t * in_row;
+    const int kvh = is_q ? 0 : (is_k ? head - p.nh : head - p.nh - p.nkv);
+    const T* src = is_q ? tok + (size_t)head * d : (is_k ? tok + (size_t)(p.nh + kvh) * d : tok + (size_t)(p.nh + p.nkv) * d + (size_t)kvh * dv);
 
     size_t cache_row = 0;
     if (!is_q) {
         const int block = p.block_table[(size_t)slot * p.table_stride + pos / p.block_tokens];
-        const int kvh = is_k ? head - p.nh : head - p.nh - p.nkv;
-        cache_row = (((size_t)block * p.nkv + kvh) * p.block_tokens + (pos % p.block_tokens)) * d;
+        cache_row = ((size_t)block * p.nkv + kvh) * p.block_tokens + (pos % p.block_tokens);
     }
     if (!is_q && !is_k) {  // value head: a plain copy into the cache
-        T* dst = (T*)p.v_cache + cache_row;
-        for (int c = lane; c < d; c += 32) dst[c] = src[c];
+        T* dst = (T*)p.v_cache + cache_row * dv;
+        for (int c = lane; c < dv; c += 32) dst[c] = src[c];
         return;
     }
+    const TG* gain = (const TG*)(is_q ? p.q_gain : p.k_gain);
+    const int mode = gain ? p.norm_mode : NORM_NONE;
     for (int c = lane; c < d; c += 32) row[c] = to_float(src[c]);
     __syncwarp();
+    if (mode == NORM_HEAD_BEFORE || mode == NORM_ALL_BEFORE) {
+        float ss = 0.f;
+        int n = d;
+        if (mode == NORM_HEAD_BEFORE) {
+            for (int c = lane; c < d; c += 32) ss = fmaf(row[c], row[c], ss);
+        } else {
+            // over the token's whole projection (all heads of q, or all of k), read in one fixed order by every head's warp
+            const T* all = is_q ? tok : tok + (size_t)p.nh * d;
+            n = (is_q ? p.nh : p.nkv) * d;
+            for (int c = lane; c < n; c += 32) { const float v = to_float(all[c]); ss = fmaf(v, v, ss); }
+            gain += (size_t)(is_q ? head : kvh) * d;
+        }
+        ss = warp_sum(ss);
+        const float scale = 1.0f / sqrtf(ss / (float)n + p.eps);
+        for (int c = lane; c < d; c += 32) row[c] = row[c] * scale * to_float(gain[c]);
+        __syncwarp();
+    }
     for (int i = lane; i < half; i += 32) {
         const float angle = (float)pos * p.inv_freq[i];
         float sn, cs;
@@ -81,18 +111,17 @@ rope_kv_kernel(RopeKvParams p, int tokens) {
         row[i + half] = x0 * sn + x1 * cs;
     }
     __syncwarp();
-    const TG* gain = (const TG*)(is_q ? p.q_gain : p.k_gain);
     float scale = 1.f;
-    if (gain) {
+    if (mode == NORM_HEAD_AFTER) {
         float ss = 0.f;
         for (int c = lane; c < d; c += 32) ss = fmaf(row[c], row[c], ss);
         ss = warp_sum(ss);
         scale = 1.0f / sqrtf(ss / (float)d + p.eps);
     }
-    T* dst = is_q ? (T*)p.q_out + ((size_t)t * p.nh + head) * d : (T*)p.k_cache + cache_row;
+    T* dst = is_q ? (T*)p.q_out + ((size_t)t * p.nh + head) * d : (T*)p.k_cache + cache_row * d;
     for (int c = lane; c < d; c += 32) {
         float v = row[c];
-        if (gain) v = v * scale * to_float(gain[c]);
+        if (mode == NORM_HEAD_AFTER) v = v * scale * to_float(gain[c]);
         dst[c] = from_float<T>(v);
     }
 }
@@ -190,6 +219,35 @@ HYMT2_API int hymt2_rope_angles(float* out, const int* token_pos, const float* i
     return hymt2_check_launch("rope_angles");
 }
 
+// The general entry: value heads of dv entries, the norm's place and reach (norm_mode, see the top of the file), and
+// inputs that hold queries only (has_kv 0; nothing is appended then).
+HYMT2_API int hymt2_rope_kv_general(const void* qkv, void* q_out, void* k_cache, void* v_cache, int dtype,
+                                    const int* block_table, int table_stride, int block_tokens,
+                                    const int* token_seq, const int* token_pos, const int* slot_ids,
+                                    const float* inv_freq, int rope_dim, const void* q_gain, const void* k_gain,
+                                    int gain_dtype, float eps, int tokens, int nh, int nkv, int d, int dv, int norm_mode,
+                                    int has_kv, int write_kv, cudaStream_t stream) {
+    if (tokens == 0) return HYMT2_OK;
+    HYMT2_REQUIRE(tokens > 0 && nh > 0 && nkv > 0 && d > 0 && dv > 0, "rope_kv: bad sizes");
+    HYMT2_REQUIRE(rope_dim >= 0 && rope_dim <= d && rope_dim % 2 == 0, "rope_kv: rope_dim %d must be even and <= head_dim %d", rope_dim, d);
+    HYMT2_REQUIRE(rope_dim == 0 || inv_freq, "rope_kv: rope_dim %d needs a frequency table", rope_dim);
+    HYMT2_REQUIRE(norm_mode >= NORM_NONE && norm_mode <= NORM_ALL_BEFORE, "rope_kv: unknown norm mode %d", norm_mode);
+    HYMT2_REQUIRE(norm_mode == NORM_NONE || (q_gain != nullptr && (k_gain != nullptr || !has_kv)), "rope_kv: a norm needs its gains");
+    HYMT2_REQUIRE(block_tokens > 0, "rope_kv: block_tokens must be positive");
+    if (!has_kv) write_kv = 0;
+    RopeKvParams p{qkv, q_out, k_cache, v_cache, block_table, token_seq, token_pos, slot_ids, inv_freq,
+                   norm_mode ? q_gain : nullptr, norm_mode ? k_gain : nullptr, table_stride, block_tokens, nh, nkv, d, rope_dim,
+                   write_kv, eps, dv, norm_mode, has_kv};
+    const size_t smem = (size_t)4 * d * sizeof(float);
+    HYMT2_REQUIRE(smem <= 48 * 1024, "rope_kv: head_dim %d is too large", d);
+    const long items = (long)tokens * (nh + (has_kv ? 2 * nkv : 0));
+    HYMT2_REQUIRE((items + 3) / 4 <= 2147483647L, "rope_kv: too many (token, head) pairs");
+    const unsigned blocks = (unsigned)((items + 3) / 4);
+    HYMT2_DISPATCH_DTYPE(dtype, T, HYMT2_DISPATCH_DTYPE(gain_dtype, TG,
+        (launch_pdl(rope_kv_kernel<T, TG>, dim3(blocks), dim3(128), smem, stream, p, tokens))));
+    return hymt2_check_launch("rope_kv");
+}
+
 HYMT2_API int hymt2_rope_kv(const void* qkv, void* q_out, void* k_cache, void* v_cache, int dtype,
                             const int* block_table, int table_stride, int block_tokens,
                             const int* token_seq, const int* token_pos, const int* slot_ids,
@@ -203,7 +261,8 @@ HYMT2_API int hymt2_rope_kv(const void* qkv, void* q_out, void* k_cache, void* v
     HYMT2_REQUIRE((q_gain == nullptr) == (k_gain == nullptr), "rope_kv: q and k gains come together");
     HYMT2_REQUIRE(block_tokens > 0, "rope_kv: block_tokens must be positive");
     RopeKvParams p{qkv, q_out, k_cache, v_cache, block_table, token_seq, token_pos, slot_ids, inv_freq,
-                   q_gain, k_gain, table_stride, block_tokens, nh, nkv, d, rope_dim, write_kv, eps};
+                   q_gain, k_gain, table_stride, block_tokens, nh, nkv, d, rope_dim, write_kv, eps, d,
+                   q_gain ? NORM_HEAD_AFTER : NORM_NONE, 1};
     const size_t smem = (size_t)4 * d * sizeof(float);
     HYMT2_REQUIRE(smem <= 48 * 1024, "rope_kv: head_dim %d is too large", d);
     const long items = (long)tokens * (nh + 2 * nkv);

@@ -78,7 +78,7 @@ class DecoderModel:
                         planes[g] += 1
                 row.append(slot)
             self.slots.append(row)
-        self.groups = [GroupSpec(s.kind, s.kv_heads, s.head_dim, planes[g], s.window, s.streams) for g, s in enumerate(specs)]
+        self.groups = [GroupSpec(s.kind, s.kv_heads, s.head_dim, planes[g], s.window, s.streams, s.value_dim) for g, s in enumerate(specs)]
         self.state_bytes = offset
 
     # -- weights ------------------------------------------------------------------

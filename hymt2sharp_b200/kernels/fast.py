@@ -99,3 +99,9 @@ def try_attention(out, q, k_plane, v_plane, block_table, ctx, nh, nkv, d, scale,
                                  ops.device_status(out.device))
         return True
     return False
+
+
+def try_attention_kv(out, q, k_plane, v_plane, block_table, ctx, nh, nkv, d, dv, scale, window, sink) -> bool:
+    """The attention with values of their own width and an optional sink on the tensor cores, where a kernel takes the
+    shape; False: the caller runs the general kernel."""
+    return False

@@ -1101,3 +1101,191 @@ def rmsnorm_groups_add_norm(residual: torch.Tensor, x: torch.Tensor, gain_a: tor
     _check(_lib().hymt2_rmsnorm_groups_add_norm(_ptr(residual), _ptr(x), _ptr(gain_a), _ptr(out), c_int(dtype_code(out.dtype)), _ptr(gain_b),
                                                 c_int(dtype_code(gain_a.dtype)), c_int(rows), c_int(dim), c_int(groups), c_float(eps_a),
                                                 c_float(eps_b), _stream()), "rmsnorm_groups_add_norm")
+
+
+# -- grouped-query attention in its general form: values of another width than keys, norms before the rotation, a sink ------
+NORM_NONE, NORM_HEAD_AFTER, NORM_HEAD_BEFORE, NORM_ALL_BEFORE = 0, 1, 2, 3
+
+
+def rope_kv_general(proj: torch.Tensor, q_out: torch.Tensor, k_plane: torch.Tensor | None, v_plane: torch.Tensor | None,
+                    block_table: torch.Tensor, block_tokens: int, token_seq: torch.Tensor, token_pos: torch.Tensor,
+                    slot_ids: torch.Tensor, inv_freq: torch.Tensor | None, rope_dim: int, q_gain: torch.Tensor | None,
+                    k_gain: torch.Tensor | None, norm_mode: int, eps: float, nh: int, nkv: int, d: int, dv: int, has_kv: bool) -> None:
+    """Norm, rotation and cache append for a projection proj[T, nh*d + nkv*(d + dv)] (queries, keys, values), or
+    proj[T, nh*d] with `has_kv` False (queries only).  norm_mode: NORM_NONE; NORM_HEAD_AFTER (per head, after the rotation, gains
+    of d entries); NORM_HEAD_BEFORE (per head, before it); NORM_ALL_BEFORE (over the token's whole q or k projection, before
+    the rotation, gains as wide as the projection).  k_plane [blocks, nkv, block_tokens, d] and v_plane [.., dv], or None to
+    append nothing."""
+    _need(proj, "proj", None, 2); _need(q_out, "q_out", proj.dtype, 2)
+    T = q_out.shape[0]
+    cols = nh * d + (nkv * (d + dv) if has_kv else 0)
+    if proj.shape[1] != cols or q_out.shape[1] != nh * d or proj.shape[0] < T:
+        raise KernelError(f"rope_kv: shapes proj {tuple(proj.shape)} q_out {tuple(q_out.shape)} for nh={nh} nkv={nkv} d={d} dv={dv}")
+    write = k_plane is not None and has_kv
+    if write:
+        for t, n, w in ((k_plane, "k_plane", d), (v_plane, "v_plane", dv)):
+            _need(t, n, proj.dtype, 4)
+            if t.shape[1:] != (nkv, block_tokens, w):
+                raise KernelError(f"rope_kv: {n} is {tuple(t.shape)}, expected [blocks, {nkv}, {block_tokens}, {w}]")
+    _need(block_table, "block_table", torch.int32, 2)
+    for t, n in ((token_seq, "token_seq"), (token_pos, "token_pos"), (slot_ids, "slot_ids")):
+        _need(t, n, torch.int32, 1)
+    if inv_freq is not None:
+        _need(inv_freq, "inv_freq", torch.float32, 1)
+        if inv_freq.shape[0] != rope_dim // 2:
+            raise KernelError("rope_kv: inv_freq must hold rope_dim/2 values")
+    gain_dtype = F32
+    if norm_mode != NORM_NONE:
+        _need(q_gain, "q_gain", None, 1)
+        gain_dtype = dtype_code(q_gain.dtype)
+        wide = norm_mode == NORM_ALL_BEFORE
+        if q_gain.shape[0] != (nh * d if wide else d):
+            raise KernelError(f"rope_kv: the q gain holds {q_gain.shape[0]} entries")
+        if has_kv:
+            _need(k_gain, "k_gain", q_gain.dtype, 1)
+            if k_gain.shape[0] != (nkv * d if wide else d):
+                raise KernelError(f"rope_kv: the k gain holds {k_gain.shape[0]} entries")
+    _check(_lib().hymt2_rope_kv_general(_ptr(proj), _ptr(q_out), _ptr(k_plane if write else None), _ptr(v_plane if write else None),
+                                        c_int(dtype_code(proj.dtype)), _ptr(block_table), c_int(block_table.stride(0)),
+                                        c_int(block_tokens), _ptr(token_seq), _ptr(token_pos), _ptr(slot_ids), _ptr(inv_freq),
+                                        c_int(rope_dim), _ptr(q_gain), _ptr(k_gain if has_kv else None), c_int(gain_dtype), c_float(eps),
+                                        c_int(T), c_int(nh), c_int(nkv), c_int(d), c_int(dv), c_int(norm_mode), c_int(1 if has_kv else 0),
+                                        c_int(1 if write else 0), _stream()), "rope_kv")
+
+
+def attention_simt_kv(out: torch.Tensor, q: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tensor,
+                      block_table: torch.Tensor, cu_seqlens: torch.Tensor, slot_ids: torch.Tensor, kv_lens: torch.Tensor, batch: int,
+                      max_new_tokens: int, nh: int, nkv: int, d: int, dv: int, scale: float, window: int = 0, sink: bool = False,
+                      split_keys: int = 0, max_splits: int = 0, part_acc: torch.Tensor | None = None,
+                      part_ml: torch.Tensor | None = None, status: torch.Tensor | None = None) -> None:
+    """attention_simt with keys of d and values of dv entries a head (out [T, nh * dv]), and optionally a sink: one more
+    term in the softmax's denominator, of score 0 and without a value.  Scratch of a split run: attention_simt_scratch with dv."""
+    if status is None:
+        status = device_status(out.device)
+    _need(out, "out", None, 2); _need(q, "q", out.dtype, 2)
+    _need(k_plane, "k_plane", out.dtype, 4); _need(v_plane, "v_plane", out.dtype, 4)
+    T = out.shape[0]
+    block_tokens = k_plane.shape[2]
+    if out.shape[1] != nh * dv or q.shape[1] != nh * d or q.shape[0] < T or k_plane.shape[1] != nkv or k_plane.shape[3] != d \
+            or v_plane.shape != (*k_plane.shape[:3], dv):
+        raise KernelError(f"attention: shapes out {tuple(out.shape)} q {tuple(q.shape)} k {tuple(k_plane.shape)} v {tuple(v_plane.shape)}")
+    _need(block_table, "block_table", torch.int32, 2)
+    for t, n in ((cu_seqlens, "cu_seqlens"), (slot_ids, "slot_ids"), (kv_lens, "kv_lens")):
+        _need(t, n, torch.int32, 1)
+    if split_keys > 0:
+        need_acc, need_ml = attention_simt_scratch(T, nh, dv, max_splits)
+        _need(part_acc, "part_acc", torch.float32); _need(part_ml, "part_ml", torch.float32)
+        if part_acc.numel() < need_acc or part_ml.numel() < need_ml:
+            raise KernelError("attention: the split scratch is too small")
+    _check(_lib().hymt2_attention_simt_kv(_ptr(out), _ptr(q), _ptr(k_plane), _ptr(v_plane), c_int(dtype_code(out.dtype)),
+                                          _ptr(block_table), c_int(block_table.stride(0)), c_int(block_tokens), _ptr(cu_seqlens),
+                                          _ptr(slot_ids), _ptr(kv_lens), c_int(batch), c_int(T), c_int(max_new_tokens), c_int(nh),
+                                          c_int(nkv), c_int(d), c_int(dv), c_float(scale), c_int(window), c_int(1 if sink else 0),
+                                          c_int(split_keys), c_int(max_splits), _ptr(part_acc), _ptr(part_ml), _stream(), _ptr(status)),
+           "attention_simt", 2 if split_keys > 0 else 1)
+
+
+# -- small steps ---------------------------------------------------------------------------------------------------------------
+def relu_squared(out: torch.Tensor, x: torch.Tensor) -> None:
+    """out = max(x, 0)^2."""
+    _need(out, "out", x.dtype); _need(x, "x")
+    if out.shape != x.shape:
+        raise KernelError("relu_squared: shapes differ")
+    _check(_lib().hymt2_relu_squared(_ptr(out), _ptr(x), c_int(dtype_code(x.dtype)), c_long(x.numel()), _stream()), "relu_squared")
+
+
+def convert(out: torch.Tensor, x: torch.Tensor) -> None:
+    """out = x rounded to out's type."""
+    _need(out, "out"); _need(x, "x")
+    if out.shape != x.shape:
+        raise KernelError("convert: shapes differ")
+    _check(_lib().hymt2_convert(_ptr(out), c_int(dtype_code(out.dtype)), _ptr(x), c_int(dtype_code(x.dtype)), c_long(x.numel()), _stream()),
+           "convert")
+
+
+def rmsnorm_add_then_rows(residual: torch.Tensor, x: torch.Tensor, gain: torch.Tensor, eps: float, out: torch.Tensor, groups: int = 1) -> None:
+    """residual (float32) += norm(x); out = the new rows rounded to out's type: the norm behind one sublayer, and the input of a
+    next sublayer that reads the residual as it is."""
+    _need(residual, "residual", torch.float32, 2); _need(x, "x", torch.float32, 2); _need(out, "out", None, 2); _need(gain, "gain", None, 1)
+    rows, dim = residual.shape
+    if x.shape != residual.shape or out.shape != residual.shape or gain.shape[0] != dim or dim % groups:
+        raise KernelError(f"rmsnorm_add_then_rows: shapes residual {tuple(residual.shape)} x {tuple(x.shape)} out {tuple(out.shape)}")
+    _check(_lib().hymt2_rmsnorm_groups_add_norm(_ptr(residual), _ptr(x), _ptr(gain), _ptr(out), c_int(dtype_code(out.dtype)), _ptr(None),
+                                                c_int(dtype_code(gain.dtype)), c_int(rows), c_int(dim), c_int(groups), c_float(eps),
+                                                c_float(eps), _stream()), "rmsnorm_groups_add_norm")
+
+
+# -- a mixture of experts ---------------------------------------------------------------------------------------------------------
+EPILOGUE_RELU_SQUARED = 3
+_group_tile = None
+
+
+def gemm_group_tile() -> int:
+    """Rows of a tile of the grouped product on CUDA cores: an expert's segment of sorted rows is padded to whole tiles."""
+    global _group_tile
+    if _group_tile is None:
+        _group_tile = int(_lib().hymt2_gemm_simt_group_tile())
+    return _group_tile
+
+
+def moe_route(chosen: torch.Tensor, weight: torch.Tensor, logits: torch.Tensor, correction: torch.Tensor | None) -> None:
+    """From router outputs logits [T, R] (float32): scores = softmax over all R; chosen [T, top] (int32) = the `top` largest of
+    score + correction, best first, ties to the lower index; weight [T, top] (float32) = their scores, as they are."""
+    _need(logits, "logits", torch.float32, 2); _need(chosen, "chosen", torch.int32, 2); _need(weight, "weight", torch.float32, 2)
+    T, R = logits.shape
+    top = chosen.shape[1]
+    if chosen.shape[0] != T or weight.shape != chosen.shape or not (0 < top <= R):
+        raise KernelError(f"moe_route: shapes logits {tuple(logits.shape)} chosen {tuple(chosen.shape)} weight {tuple(weight.shape)}")
+    _f32(correction, "correction", R)
+    _check(_lib().hymt2_moe_route(_ptr(chosen), _ptr(weight), _ptr(logits), _ptr(correction), c_int(T), c_int(R), c_int(top), _stream()),
+           "moe_route")
+
+
+def moe_tiles(tokens: int, top: int, experts: int, tile: int) -> int:
+    """Row tiles that the sorted list of a step can need at most: every expert's segment is padded to whole tiles."""
+    return -(-(tokens * top + experts * (tile - 1)) // tile) if experts else 1
+
+
+def moe_place(pair_row: torch.Tensor, row_token: torch.Tensor, tile_group: torch.Tensor, counts: torch.Tensor, chosen: torch.Tensor,
+              experts: int, tile: int) -> None:
+    """Sorts the (token, choice) pairs of chosen [T, top] by expert, tokens in order inside an expert, each expert's rows padded
+    to whole tiles: pair_row [T, top] = a pair's row in the sorted list (-1: it names an identity expert, index >= experts),
+    row_token [tiles * tile] = the token of a sorted row (-1: padding), tile_group [tiles] = the expert of a row tile (-1: not
+    in use).  counts [max(experts, 1)] is scratch."""
+    for t, n in ((pair_row, "pair_row"), (row_token, "row_token"), (tile_group, "tile_group"), (counts, "counts"), (chosen, "chosen")):
+        _need(t, n, torch.int32)
+    T, top = chosen.shape
+    tiles = tile_group.numel()
+    if pair_row.shape != chosen.shape or row_token.numel() < tiles * tile or tiles < moe_tiles(T, top, experts, tile) \
+            or counts.numel() < max(experts, 1):
+        raise KernelError("moe_place: a buffer is too small")
+    _check(_lib().hymt2_moe_place(_ptr(pair_row), _ptr(row_token), _ptr(tile_group), _ptr(counts), _ptr(chosen), c_int(T), c_int(top),
+                                  c_int(experts), c_int(tile), c_int(tiles), _stream()), "moe_place", 2)
+
+
+def gemm_simt_grouped(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, tile_group: torch.Tensor, row_token: torch.Tensor,
+                      gather: bool, epilogue: int = EPILOGUE_STORE) -> None:
+    """out[r] = epilogue(a[source(r)] @ w[tile_group[r // tile]]^T) for the sorted rows r of moe_place: w [experts, N, K];
+    source(r) = row_token[r] with `gather` (a holds one row per token), r itself otherwise (a holds sorted rows); padding
+    rows and unused tiles are skipped.  Epilogues: EPILOGUE_STORE, EPILOGUE_RELU_SQUARED."""
+    _need(out, "out", None, 2); _need(a, "a", None, 2); _need(w, "w", None, 3)
+    _need(tile_group, "tile_group", torch.int32, 1); _need(row_token, "row_token", torch.int32, 1)
+    tiles, tile = tile_group.numel(), gemm_group_tile()
+    N, K = w.shape[1], w.shape[2]
+    if out.shape != (tiles * tile, N) or a.shape[1] != K or row_token.numel() < tiles * tile or (not gather and a.shape[0] < tiles * tile):
+        raise KernelError(f"gemm_simt_grouped: shapes out {tuple(out.shape)} a {tuple(a.shape)} w {tuple(w.shape)} tiles {tiles}")
+    _check(_lib().hymt2_gemm_simt_grouped(_ptr(out), c_int(dtype_code(out.dtype)), _ptr(a), c_int(dtype_code(a.dtype)), _ptr(w),
+                                          c_int(dtype_code(w.dtype)), _ptr(tile_group), _ptr(row_token), c_int(1 if gather else 0),
+                                          c_int(tiles), c_int(N), c_int(K), c_long(a.stride(0)), c_long(out.stride(0)), c_long(N * K),
+                                          c_int(epilogue), _stream()), "gemm_simt_grouped")
+
+
+def moe_combine(out: torch.Tensor, y: torch.Tensor, x: torch.Tensor, pair_row: torch.Tensor, weight: torch.Tensor, add: bool = False) -> None:
+    """out[t] (float32) = (out[t] if `add`) + sum_k weight[t, k] * (y[pair_row[t, k]] if pair_row[t, k] >= 0 else x[t]), k in order."""
+    _need(out, "out", torch.float32, 2); _need(y, "y", torch.float32, 2); _need(x, "x", None, 2)
+    _need(pair_row, "pair_row", torch.int32, 2); _need(weight, "weight", torch.float32, 2)
+    T, H = out.shape
+    if x.shape != out.shape or y.shape[1] != H or pair_row.shape[0] != T or weight.shape != pair_row.shape:
+        raise KernelError(f"moe_combine: shapes out {tuple(out.shape)} y {tuple(y.shape)} x {tuple(x.shape)} pairs {tuple(pair_row.shape)}")
+    _check(_lib().hymt2_moe_combine(_ptr(out), _ptr(y), _ptr(x), c_int(dtype_code(x.dtype)), _ptr(pair_row), _ptr(weight), c_int(T), c_int(H),
+                                    c_int(pair_row.shape[1]), c_int(1 if add else 0), _stream()), "moe_combine")

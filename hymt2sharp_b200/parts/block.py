@@ -3,6 +3,7 @@
 float32; the normed activations have the engine's compute type."""
 from __future__ import annotations
 
+from ..kernels import ops
 from .base import PartSpec, Prenormed, build_part, register_part
 
 
@@ -73,17 +74,22 @@ class SandwichBlock:
     sequence, which this block asks the model for beside its mixer's: cache_needs() / state_bytes() have the mixer's
     entry first, then one entry for each convolution it holds.  A sublayer's output is collected in a float32 buffer and
     joins the residual through the norm after it.  Mixers and feed-forwards add into what they are given, so the buffer
-    starts from zeros; a part that says `can_store = True` takes `store=True` and overwrites it instead (no zeroing)."""
+    starts from zeros; a part that says `can_store = True` takes `store=True` and overwrites it instead (no zeroing).
 
-    def __init__(self, norm1: PartSpec, mixer: PartSpec, norm1_after: PartSpec, norm2: PartSpec | None = None,
+    The norms in FRONT are optional (`norm1` / `norm2` None): such a sublayer reads the residual rows themselves, and the norm
+    is on its output only, x += norm1b(mixer(x)).  In an engine whose compute type is not float32 the rows are rounded once;
+    the kernel of the norm behind a sublayer writes that rounding beside the new residual, also for the block that runs next
+    (left in `ctx.shared["residual_rows"]`)."""
+
+    def __init__(self, norm1: PartSpec | None, mixer: PartSpec, norm1_after: PartSpec, norm2: PartSpec | None = None,
                  feed_forward: PartSpec | None = None, norm2_after: PartSpec | None = None, conv1: dict | None = None,
                  conv2: dict | None = None):
         from .conv import ShortConv
-        self.norm1 = build_part("norm", norm1)
+        self.norm1 = build_part("norm", norm1) if norm1 is not None else None
         self.mixer = build_part("mixer", mixer)
         self.norm1_after = build_part("norm", norm1_after)
         self.feed_forward = build_part("feed_forward", feed_forward) if feed_forward is not None else None
-        self.norm2 = build_part("norm", norm2) if feed_forward is not None else None
+        self.norm2 = build_part("norm", norm2) if feed_forward is not None and norm2 is not None else None
         self.norm2_after = build_part("norm", norm2_after) if feed_forward is not None else None
         self.conv1 = ShortConv(add_input=True, **conv1) if conv1 is not None else None
         self.conv2 = ShortConv(add_input=True, **conv2) if conv2 is not None and feed_forward is not None else None
@@ -122,7 +128,13 @@ class SandwichBlock:
         import torch
         conv_slots = list(slots[1:])
         ctx.weights_ahead = ctx.norm_ahead = None
-        h = self.norm1.forward(residual, ctx, ctx.dtype, fresh=True)
+        left = ctx.shared.pop("residual_rows", None)
+        if self.norm1 is not None:
+            h = self.norm1.forward(residual, ctx, ctx.dtype, fresh=True)
+        elif left is not None and left[0] is residual and left[1].dtype == ctx.dtype:
+            h = left[1]                      # what the block in front wrote beside its last change of the residual
+        else:
+            h = self._rows(residual, ctx)
         if self.conv1 is not None:
             h = self.conv1.forward(h, ctx, conv_slots.pop(0))
         if getattr(self.mixer, "can_store", False):
@@ -133,9 +145,12 @@ class SandwichBlock:
             self.mixer.forward(h, branch, ctx, slots[0])
         ctx.prenormed = None
         if self.feed_forward is None:
-            self.norm1_after.add_into(branch, residual)
+            self._last(self.norm1_after, branch, residual, ctx)
             return
-        h = self.norm1_after.add_into_then(branch, residual, self.norm2, ctx.dtype)
+        if self.norm2 is not None:
+            h = self.norm1_after.add_into_then(branch, residual, self.norm2, ctx.dtype)
+        else:
+            h = self.norm1_after.add_into_then_rows(branch, residual, ctx.dtype)
         if self.conv2 is not None:
             h = self.conv2.forward(h, ctx, conv_slots.pop(0))
         if getattr(self.feed_forward, "can_store", False):
@@ -144,7 +159,25 @@ class SandwichBlock:
             branch.zero_()
             self.feed_forward.forward(h, branch, ctx)
         ctx.prenormed = None
-        self.norm2_after.add_into(branch, residual)
+        self._last(self.norm2_after, branch, residual, ctx)
+
+    @staticmethod
+    def _rows(residual, ctx):
+        """The residual rows as a sublayer without a norm in front reads them: themselves, or rounded to the compute type."""
+        import torch
+        if ctx.dtype == residual.dtype:
+            return residual
+        h = torch.empty(residual.shape, dtype=ctx.dtype, device=residual.device)
+        ops.convert(h, residual)
+        return h
+
+    def _last(self, norm, branch, residual, ctx) -> None:
+        """The block's last change of the residual.  A block whose own first sublayer reads plain rows expects the same of the
+        block behind it and leaves the rounded rows for it."""
+        if self.norm1 is None and ctx.dtype != residual.dtype:
+            ctx.shared["residual_rows"] = (residual, norm.add_into_then_rows(branch, residual, ctx.dtype))
+        else:
+            norm.add_into(branch, residual)
 
 
 register_part("block", "sandwich", SandwichBlock)

@@ -1,7 +1,8 @@
 """Dense feed-forward with one up and one down projection: residual += W_down act(W_up x).
 
 Activations: "xielu", with two learned numbers (p, q) stored as a tensor of two values:
-act(z) = softplus(p) z^2 + z/2 for z > 0, and (1/2 + softplus(q)) (exp(z) - 1 - z) + z/2 for z <= 0.
+act(z) = softplus(p) z^2 + z/2 for z > 0, and (1/2 + softplus(q)) (exp(z) - 1 - z) + z/2 for z <= 0;
+"relu2", the square of relu, act(z) = max(z, 0)^2, which has no tensor of its own.
 """
 from __future__ import annotations
 
@@ -12,7 +13,7 @@ from ..weights.loader import TensorSpec
 from .base import register_part
 from .linear import Linear, compute_form
 
-ACTIVATIONS = ("xielu",)
+ACTIVATIONS = ("xielu", "relu2")
 
 
 class DenseMLP:
@@ -28,22 +29,28 @@ class DenseMLP:
 
     def tensors(self):
         n = self.names
-        return {n["u"]: TensorSpec((self.intermediate, self.hidden)), n["d"]: TensorSpec((self.hidden, self.intermediate)),
-                n["a"]: TensorSpec((2,))}
+        t = {n["u"]: TensorSpec((self.intermediate, self.hidden)), n["d"]: TensorSpec((self.hidden, self.intermediate))}
+        if self.activation == "xielu":
+            t[n["a"]] = TensorSpec((2,))
+        return t
 
     def load(self, weights, device, dtype):
         n = self.names
         self.up = Linear(compute_form(weights[n["u"]], device, dtype), role="up")
         self.down = Linear(compute_form(weights[n["d"]], device, dtype), ops.EPILOGUE_ACCUMULATE, role="down")
         self.down_store = Linear(self.down.weight, ops.EPILOGUE_STORE, role="down")
-        self.pq = weights[n["a"]].to(device).float().contiguous()
+        if self.activation == "xielu":
+            self.pq = weights[n["a"]].to(device).float().contiguous()
 
     def first_weights(self):
         return self.up.weight if self.up is not None else None
 
     def forward(self, x, residual: torch.Tensor, ctx, store: bool = False) -> None:
         z = self.up(x, ctx=ctx)
-        ops.xielu(z, z, self.pq)
+        if self.activation == "xielu":
+            ops.xielu(z, z, self.pq)
+        else:
+            ops.relu_squared(z, z)
         if store:
             self.down_store(z, out=residual)
         else:

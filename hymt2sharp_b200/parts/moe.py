@@ -1,0 +1,103 @@
+"""A mixture of small feed-forward experts with a router: residual += sum over a token's chosen experts of weight * expert(x).
+
+The router's outputs z = W_router x are float32 (float32 sums of the products in both engines); the scores are their
+softmax over ALL outputs.  The first `experts` outputs name experts with tensors, expert(x) = W_down act(W_up x); the last
+`identity` outputs name identity experts, whose output is x itself.  The `top` outputs with the largest score + correction
+are chosen (`correction`: a stored vector, one entry per output; None: none); a chosen output's weight is its score, without
+the correction and not renormalised.  A shared expert (any feed-forward part) runs for every token with weight 1.
+
+How a step runs: router product; `moe_route` (softmax, choice); `moe_place` sorts the (token, choice) pairs by expert, each
+expert's rows padded to whole row tiles; one grouped product per projection over the sorted rows (the first gathers its
+input rows by token, its epilogue is the activation); `moe_combine` adds a token's rows up in the order they were chosen.
+Nothing uses atomics and every sum has a fixed order, so a token's result does not depend on the other tokens of the step.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+from ..weights.loader import TensorSpec
+from .base import PartSpec, build_part, register_part
+from .linear import Linear, compute_form
+
+ACTIVATIONS = {"relu2": ops.EPILOGUE_RELU_SQUARED}
+
+
+class RoutedExperts:
+    graph_safe = True  # its forward only launches kernels on the current stream
+    can_store = True   # forward(..., store=True) overwrites `residual` with its output instead of adding to it
+
+    def __init__(self, hidden: int, experts: int, identity: int, top: int, intermediate: int, activation: str, router: str,
+                 up_proj: str, down_proj: str, correction: str | None = None, shared: PartSpec | None = None):
+        """`up_proj` / `down_proj`: the tensor names of expert e with `{}` in place of e."""
+        if activation not in ACTIVATIONS:
+            raise ValueError(f"activation '{activation}' is not known (known: {', '.join(ACTIVATIONS)})")
+        if experts < 0 or identity < 0 or not (0 < top <= experts + identity):
+            raise ValueError(f"{top} of {experts} + {identity} experts cannot be chosen")
+        self.hidden, self.experts, self.identity, self.top = int(hidden), int(experts), int(identity), int(top)
+        self.intermediate, self.activation = int(intermediate), activation
+        self.names = dict(r=router, c=correction, u=up_proj, d=down_proj)
+        self.shared = build_part("feed_forward", shared) if shared is not None else None
+        self.router = self.correction = self.up = self.down = None
+
+    @property
+    def outputs(self) -> int:
+        return self.experts + self.identity
+
+    def tensors(self):
+        n = self.names
+        t = {n["r"]: TensorSpec((self.outputs, self.hidden))}
+        if n["c"] is not None:
+            t[n["c"]] = TensorSpec((self.outputs,))
+        for e in range(self.experts):
+            t[n["u"].format(e)] = TensorSpec((self.intermediate, self.hidden))
+            t[n["d"].format(e)] = TensorSpec((self.hidden, self.intermediate))
+        if self.shared is not None:
+            t.update(self.shared.tensors())
+        return t
+
+    def load(self, weights, device, dtype):
+        n = self.names
+        self.router = Linear(compute_form(weights[n["r"]], device, dtype), role="router")
+        self.correction = weights[n["c"]].to(device).float().contiguous() if n["c"] is not None else None
+        if self.experts:
+            # every expert's matrix of a kind in one tensor [experts, out, in]: a grouped product picks its expert by index
+            self.up = compute_form(torch.stack([weights[n["u"].format(e)] for e in range(self.experts)]), device, dtype)
+            self.down = compute_form(torch.stack([weights[n["d"].format(e)] for e in range(self.experts)]), device, dtype)
+        if self.shared is not None:
+            self.shared.load(weights, device, dtype)
+
+    def first_weights(self):
+        return self.router.weight if self.router is not None else None
+
+    def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx, store: bool = False) -> None:
+        T, dev = x.shape[0], x.device
+        logits = self.router(x, out_dtype=torch.float32, ctx=ctx)
+        chosen = torch.empty((T, self.top), dtype=torch.int32, device=dev)
+        weight = torch.empty((T, self.top), dtype=torch.float32, device=dev)
+        ops.moe_route(chosen, weight, logits, self.correction)
+        tile = ops.gemm_group_tile()
+        tiles = ops.moe_tiles(T, self.top, self.experts, tile)
+        ints = torch.empty(T * self.top + tiles * tile + tiles + max(self.experts, 1), dtype=torch.int32, device=dev)
+        pair_row = ints[: T * self.top].view(T, self.top)
+        row_token = ints[T * self.top: T * self.top + tiles * tile]
+        tile_group = ints[T * self.top + tiles * tile: T * self.top + tiles * tile + tiles]
+        counts = ints[T * self.top + tiles * tile + tiles:]
+        ops.moe_place(pair_row, row_token, tile_group, counts, chosen, self.experts, tile)
+        if self.experts:
+            act = torch.empty((tiles * tile, self.intermediate), dtype=x.dtype, device=dev)
+            ops.tag = "experts_up"
+            ops.gemm_simt_grouped(act, x, self.up, tile_group, row_token, True, ACTIVATIONS[self.activation])
+            y = torch.empty((tiles * tile, self.hidden), dtype=torch.float32, device=dev)
+            ops.tag = "experts_down"
+            ops.gemm_simt_grouped(y, act, self.down, tile_group, row_token, False, ops.EPILOGUE_STORE)
+            ops.tag = None
+        else:
+            y = torch.empty((1, self.hidden), dtype=torch.float32, device=dev)   # never read: every pair names an identity expert
+        ops.moe_combine(residual, y, x, pair_row, weight, add=not store)
+        if self.shared is not None:
+            self.shared.forward(x, residual, ctx)
+        ctx.prenormed = None
+
+
+register_part("feed_forward", "routed_experts", RoutedExperts)

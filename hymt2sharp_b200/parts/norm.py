@@ -63,4 +63,15 @@ class RMSNorm:
         return following.forward(residual, None, out_dtype, fresh=True)
 
 
+    def add_into_then_rows(self, x: torch.Tensor, residual: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+        """add_into, and the new rows in `out_dtype` for a sublayer that reads the residual as it is (no norm in front of it):
+        the residual itself where that is its type, else its rounding, written by the same kernel."""
+        if out_dtype == residual.dtype:
+            self.add_into(x, residual)
+            return residual
+        out = torch.empty(residual.shape, dtype=out_dtype, device=residual.device)
+        ops.rmsnorm_add_then_rows(residual, x, self.gain, self.eps, out, self.groups)
+        return out
+
+
 register_part("norm", "rmsnorm", RMSNorm)

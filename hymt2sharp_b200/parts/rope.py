@@ -109,3 +109,50 @@ class YarnInterleavedRotary:
 
 
 register_part("position", "yarn_interleaved", YarnInterleavedRotary)
+
+
+class WavelengthScaledRotary:
+    """Rotate-half rotary encoding whose frequencies are scaled by their wavelength (the long-context rule of Llama 3.1).
+
+    Of a head's first `dims` entries, (i, i + dims/2) are a pair that turns by position * f_i, f_i = base^(-2i/dims).
+    With `scaling` = (factor, low, high, original): a frequency whose wavelength l = 2 pi / f is shorter than original / high
+    stays; one longer than original / low becomes f / factor; between the two, with s = (original / l - low) / (high - low),
+    it becomes (1 - s) f / factor + s f.  The table is computed on the host in float64 and rounded to float32 once; the angle is
+    the float32 product position * f_i in the kernels, which take the table as the rotate-half epilogue.
+    """
+
+    def __init__(self, dims: int, base: float, scaling: dict | None = None):
+        if dims % 2 or dims < 0:
+            raise ValueError(f"{dims} rotated entries: the number must be even")
+        self.dims, self.base, self.scaling = int(dims), float(base), dict(scaling) if scaling else None
+        f = [self.base ** (-2.0 * i / self.dims) for i in range(self.dims // 2)]
+        if self.scaling:
+            factor, low, high, original = (float(self.scaling[k]) for k in ("factor", "low", "high", "original"))
+            short, long = original / high, original / low
+            for i, fi in enumerate(f):
+                wavelength = 2.0 * math.pi / fi
+                if wavelength > long:
+                    f[i] = fi / factor
+                elif wavelength >= short:
+                    s = (original / wavelength - low) / (high - low)
+                    f[i] = (1.0 - s) * fi / factor + s * fi
+        self._host = np.asarray(f, dtype=np.float64).astype(np.float32)
+        self.inv_freq = None
+
+    def tensors(self):
+        return {}
+
+    def load(self, weights, device, dtype):
+        key = (str(torch.device(device)), self._host.tobytes())
+        if key not in _TABLES:
+            _TABLES[key] = torch.from_numpy(self._host).to(device)
+        self.inv_freq = _TABLES[key]
+
+    def kernel_epilogue(self, ctx) -> RotaryEpilogue:
+        return RotaryEpilogue(self.inv_freq if self.dims else None, self.dims)
+
+    def apply(self, qkv, ctx, heads, kv_heads, head_dim):
+        raise NotImplementedError("WavelengthScaledRotary is applied by the kernels that take a rotate-half epilogue")
+
+
+register_part("position", "wavelength_scaled_rope", WavelengthScaledRotary)
