@@ -166,7 +166,7 @@ HYMT2_API int hymt2_moe_place(int* pair_row, int* row_token, int* tile_group, in
     if (tokens == 0) return HYMT2_OK;
     HYMT2_REQUIRE(tokens > 0 && top > 0 && experts >= 0 && tile > 0, "moe_place: bad sizes");
     HYMT2_REQUIRE((long)tokens * top < (1L << 24), "moe_place: too many (token, choice) pairs");
-    HYMT2_REQUIRE((long)max_tiles * tile >= (long)tokens * top + (long)experts * (tile - 1), "moe_place: too few tiles");
+    HYMT2_REQUIRE(experts == 0 || (long)max_tiles * tile >= (long)tokens * top + (long)experts * (tile - 1), "moe_place: too few tiles");
     const int pairs = tokens * top;
     const int blocks = experts > 0 ? experts : 1;
     launch_pdl(moe_count_kernel, dim3(blocks), dim3(PLACE_THREADS), 0, stream, counts, chosen, pairs, experts);

@@ -165,3 +165,12 @@ def forward(config: dict, w: dict, tokens: list[int], layers_out: bool = False):
         after.append(x)
     logits = rms_norm(x, w["final.norm"], eps) @ w["head"].T
     return (logits, torch.stack(after)) if layers_out else logits
+
+
+def greedy(config: dict, weights: dict, prompt, new_tokens: int) -> list:
+    toks, out = list(prompt), []
+    for _ in range(new_tokens):
+        nxt = int(forward(config, weights, toks)[-1].argmax())
+        out.append(nxt)
+        toks.append(nxt)
+    return out
