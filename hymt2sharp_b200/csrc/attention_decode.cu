@@ -13,8 +13,10 @@
 // scratch; the merge kernel of attention_simt.cu folds the chunks in index order.  The chunk
 // size is a constant, so the cut depends on a key's index only.
 //
-// Takes head sizes 64 and 128 and any number of heads and groups; other shapes stay with the
-// general kernel.
+// Values may be of another width than keys (DV entries a head), and the softmax may have a sink (one more
+// term in its denominator, of score 0 and without a value), which joins when a row's chunks are folded.
+// Takes key and value sizes of 64 and 128 (in any pairing) and any number of heads and groups; other shapes stay
+// with the general kernel.
 #include "common.cuh"
 
 namespace {
@@ -34,6 +36,7 @@ struct DecodeParams {
     int* counters;                 // [rows, nkv * groups] arrivals of a row's chunks, zero between launches
     int table_stride, block_shift, nh, nkv, window, max_splits;   // block_tokens = 1 << block_shift
     float scale;
+    int sink;
 };
 
 template <int E>
@@ -57,15 +60,16 @@ __device__ __forceinline__ void unpack(const uint4 (&raw)[E / 8], float (&f)[E])
     }
 }
 
-template <int D, int G>
+template <int D, int DV, int G>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_decode_kernel(DecodeParams p) {
     constexpr int E = D / LANES_PER_KEY;   // elements of a key that one lane holds
+    constexpr int EV = DV / LANES_PER_KEY; // and of a value
     constexpr int KEYS_PER_WARP = CHUNK_KEYS / WARPS;
     constexpr int ITERS = KEYS_PER_WARP / KEYS_PER_ITER;   // 16 keys per lane group
     constexpr int PF = 4;                  // keys in flight per lane group
     __shared__ float sm_p[WARPS][KEYS_PER_WARP][G];        // scores, then softmax numerators
-    __shared__ float sm_acc[WARPS][G][D];
+    __shared__ float sm_acc[WARPS][G][DV];
     __shared__ float sm_ml[WARPS][G][2];
     pdl_launch_dependents();
     pdl_wait();
@@ -84,13 +88,15 @@ attention_decode_kernel(DecodeParams p) {
     const int* table = p.block_table + (size_t)slot * p.table_stride;
     const int warp_begin = chunk_begin + warp * KEYS_PER_WARP;
 
-    auto address = [&](int it, bool& ok) -> size_t {   // the row of this lane group's key of iteration `it`
+    auto row_of = [&](int it, bool& ok) -> size_t {   // the cache row of this lane group's key of iteration `it`
         const int key = warp_begin + it * KEYS_PER_ITER + keygrp;
         ok = key >= lo && key <= pos;
         if (!ok) return 0;
         const int block = table[key >> p.block_shift];
-        return ((((size_t)block * p.nkv + kvh) << p.block_shift) + (key & ((1 << p.block_shift) - 1))) * D + sub * E;
+        return (((size_t)block * p.nkv + kvh) << p.block_shift) + (key & ((1 << p.block_shift) - 1));
     };
+    auto address = [&](int it, bool& ok) -> size_t { return row_of(it, ok) * D + sub * E; };      // this lane's part of the key
+    auto address_v = [&](int it, bool& ok) -> size_t { return row_of(it, ok) * DV + sub * EV; };  // and of the value
 
     // ---- pass 1: scores of the warp's 64 keys; only q and the keys in flight are live --------
     float m[G];
@@ -169,34 +175,34 @@ attention_decode_kernel(DecodeParams p) {
     __syncwarp();
 
     // ---- pass 2: weighted sum of the values; only the accumulators and the values in flight ----
-    float acc[G][E];
+    float acc[G][EV];
 #pragma unroll
     for (int h = 0; h < G; h++)
 #pragma unroll
-        for (int e = 0; e < E; e++) acc[h][e] = 0.f;
+        for (int e = 0; e < EV; e++) acc[h][e] = 0.f;
     {
-        uint4 vraw[PF][E / 8];
+        uint4 vraw[PF][EV / 8];
         bool okv[PF];
 #pragma unroll
         for (int i = 0; i < PF; i++) {
-            const size_t a = address(i, okv[i]);
-            load_row<E>(p.v_cache + a, vraw[i], okv[i]);
+            const size_t a = address_v(i, okv[i]);
+            load_row<EV>(p.v_cache + a, vraw[i], okv[i]);
         }
 #pragma unroll
         for (int it = 0; it < ITERS; it++) {
             const int st = it % PF;
-            float vf[E];
-            unpack<E>(vraw[st], vf);
+            float vf[EV];
+            unpack<EV>(vraw[st], vf);
             if (it + PF < ITERS) {
-                const size_t a = address(it + PF, okv[st]);
-                load_row<E>(p.v_cache + a, vraw[st], okv[st]);
+                const size_t a = address_v(it + PF, okv[st]);
+                load_row<EV>(p.v_cache + a, vraw[st], okv[st]);
             }
             const float* pr = sm_p[warp][it * KEYS_PER_ITER + keygrp];   // 0 for keys that are not visible
 #pragma unroll
             for (int h = 0; h < G; h++) {
                 const float pj = pr[h];
 #pragma unroll
-                for (int e = 0; e < E; e++) acc[h][e] = fmaf(pj, vf[e], acc[h][e]);
+                for (int e = 0; e < EV; e++) acc[h][e] = fmaf(pj, vf[e], acc[h][e]);
             }
         }
     }
@@ -206,18 +212,18 @@ attention_decode_kernel(DecodeParams p) {
 #pragma unroll
         for (int h = 0; h < G; h++)
 #pragma unroll
-            for (int e = 0; e < E; e++) acc[h][e] += __shfl_xor_sync(0xffffffffu, acc[h][e], o);
+            for (int e = 0; e < EV; e++) acc[h][e] += __shfl_xor_sync(0xffffffffu, acc[h][e], o);
     if (keygrp == 0) {
 #pragma unroll
         for (int h = 0; h < G; h++) {
 #pragma unroll
-            for (int e = 0; e < E; e++) sm_acc[warp][h][sub * E + e] = acc[h][e];
+            for (int e = 0; e < EV; e++) sm_acc[warp][h][sub * EV + e] = acc[h][e];
             if (sub == 0) { sm_ml[warp][h][0] = m[h]; sm_ml[warp][h][1] = l[h]; }
         }
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < G * D; i += blockDim.x) {
-        const int h = i / D, x = i - h * D;
+    for (int i = threadIdx.x; i < G * DV; i += blockDim.x) {
+        const int h = i / DV, x = i - h * DV;
         float M = -INFINITY;
 #pragma unroll
         for (int w = 0; w < WARPS; w++) M = fmaxf(M, sm_ml[w][h][0]);
@@ -229,7 +235,7 @@ attention_decode_kernel(DecodeParams p) {
             a += sm_acc[w][h][x] * c;
         }
         const size_t row = ((size_t)b * p.nh + head0 + h) * p.max_splits + split;
-        p.part_acc[row * D + x] = a;
+        p.part_acc[row * DV + x] = a;
         if (x == 0) { p.part_ml[row * 2] = M; p.part_ml[row * 2 + 1] = L; }
     }
 
@@ -247,52 +253,64 @@ attention_decode_kernel(DecodeParams p) {
     __syncthreads();
     if (!last_s) return;
     __threadfence();
-    for (int i = threadIdx.x; i < G * D; i += blockDim.x) {
-        const int h = i / D, x = i - h * D;
+    for (int i = threadIdx.x; i < G * DV; i += blockDim.x) {
+        const int h = i / DV, x = i - h * DV;
         const size_t row = ((size_t)b * p.nh + head0 + h) * p.max_splits;
-        float M = -INFINITY;
+        float M = p.sink ? 0.f : -INFINITY;   // the sink is one more partial, with maximum 0 and sum 1
         for (int s = s_begin; s < s_end; s++) M = fmaxf(M, __ldcg(p.part_ml + (row + s) * 2));
-        float L = 0.f, a = 0.f;
+        float L = p.sink ? expf(-M) : 0.f, a = 0.f;
         for (int s = s_begin; s < s_end; s++) {
             const float c = expf(__ldcg(p.part_ml + (row + s) * 2) - M);
             L += __ldcg(p.part_ml + (row + s) * 2 + 1) * c;
-            a = fmaf(__ldcg(p.part_acc + (row + s) * D + x), c, a);
+            a = fmaf(__ldcg(p.part_acc + (row + s) * DV + x), c, a);
         }
-        p.out[((size_t)b * p.nh + head0 + h) * D + x] = __float2bfloat16_rn(L > 0.f ? a / L : 0.f);
+        p.out[((size_t)b * p.nh + head0 + h) * DV + x] = __float2bfloat16_rn(L > 0.f ? a / L : 0.f);
     }
 }
 
-template <int D>
+template <int D, int DV>
 int launch_d(const DecodeParams& p, int rows, int g, int splits, cudaStream_t stream) {
     const int G = g % 4 == 0 ? 4 : g % 2 == 0 ? 2 : 1;
     dim3 grid(splits, p.nkv * (g / G), rows);
-    if (G == 4) launch_pdl(attention_decode_kernel<D, 4>, grid, dim3(WARPS * 32), 0, stream, p);
-    else if (G == 2) launch_pdl(attention_decode_kernel<D, 2>, grid, dim3(WARPS * 32), 0, stream, p);
-    else launch_pdl(attention_decode_kernel<D, 1>, grid, dim3(WARPS * 32), 0, stream, p);
+    if (G == 4) launch_pdl(attention_decode_kernel<D, DV, 4>, grid, dim3(WARPS * 32), 0, stream, p);
+    else if (G == 2) launch_pdl(attention_decode_kernel<D, DV, 2>, grid, dim3(WARPS * 32), 0, stream, p);
+    else launch_pdl(attention_decode_kernel<D, DV, 1>, grid, dim3(WARPS * 32), 0, stream, p);
     return hymt2_check_launch("attention_decode");
 }
 
 }  // namespace
 
-// out, q: [rows, nh * d] bfloat16; one new token per row.  max_splits >= ceil(longest kv_len / 256);
-// part_acc holds rows*nh*max_splits*d floats, part_ml rows*nh*max_splits*2, counters rows*nh ints
+// out [rows, nh * dv], q [rows, nh * d] bfloat16; one new token per row.  max_splits >= ceil(longest kv_len / 256);
+// part_acc holds rows*nh*max_splits*dv floats, part_ml rows*nh*max_splits*2, counters rows*nh ints
 // that are zero before the first launch (the kernel leaves them zero).
-HYMT2_API int hymt2_attention_decode(void* out, const void* q, const void* k_cache, const void* v_cache,
-                                     const int* block_table, int table_stride, int block_tokens, const int* cu_seqlens,
-                                     const int* slot_ids, const int* kv_lens, int rows, int nh, int nkv, int d, float scale,
-                                     int window, int max_splits, float* part_acc, float* part_ml, int* counters,
-                                     cudaStream_t stream) {
+HYMT2_API int hymt2_attention_decode_kv(void* out, const void* q, const void* k_cache, const void* v_cache,
+                                        const int* block_table, int table_stride, int block_tokens, const int* cu_seqlens,
+                                        const int* slot_ids, const int* kv_lens, int rows, int nh, int nkv, int d, int dv, float scale,
+                                        int window, int sink, int max_splits, float* part_acc, float* part_ml, int* counters,
+                                        cudaStream_t stream) {
     if (rows == 0) return HYMT2_OK;
     HYMT2_REQUIRE(rows > 0 && nh > 0 && nkv > 0 && nh % nkv == 0, "attention_decode: bad sizes");
-    HYMT2_REQUIRE(d == 64 || d == 128, "attention_decode: head_dim %d is not taken (64 and 128 are)", d);
+    HYMT2_REQUIRE((d == 64 || d == 128) && (dv == 64 || dv == 128), "attention_decode: heads of %d and %d are not taken (64 and 128 are)", d, dv);
     HYMT2_REQUIRE(max_splits > 0 && part_acc && part_ml && counters, "attention_decode: scratch for the partials is needed");
     int block_shift = 0;
     while ((1 << block_shift) < block_tokens) block_shift++;
     HYMT2_REQUIRE((1 << block_shift) == block_tokens, "attention_decode: block_tokens %d must be a power of two", block_tokens);
     HYMT2_REQUIRE(rows <= 65535 && nkv * (nh / nkv) <= 65535, "attention_decode: grid too large");
     DecodeParams p{(const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, block_table,
-                   slot_ids, kv_lens, (__nv_bfloat16*)out, part_acc, part_ml, counters, table_stride, block_shift, nh, nkv, window, max_splits, scale};
+                   slot_ids, kv_lens, (__nv_bfloat16*)out, part_acc, part_ml, counters, table_stride, block_shift, nh, nkv, window, max_splits, scale,
+                   sink};
     const int g = nh / nkv;
     (void)cu_seqlens;
-    return d == 128 ? launch_d<128>(p, rows, g, max_splits, stream) : launch_d<64>(p, rows, g, max_splits, stream);
+    if (d == 128) return dv == 128 ? launch_d<128, 128>(p, rows, g, max_splits, stream) : launch_d<128, 64>(p, rows, g, max_splits, stream);
+    return dv == 128 ? launch_d<64, 128>(p, rows, g, max_splits, stream) : launch_d<64, 64>(p, rows, g, max_splits, stream);
+}
+
+// The classic form: values as wide as keys, no sink.
+HYMT2_API int hymt2_attention_decode(void* out, const void* q, const void* k_cache, const void* v_cache,
+                                     const int* block_table, int table_stride, int block_tokens, const int* cu_seqlens,
+                                     const int* slot_ids, const int* kv_lens, int rows, int nh, int nkv, int d, float scale,
+                                     int window, int max_splits, float* part_acc, float* part_ml, int* counters,
+                                     cudaStream_t stream) {
+    return hymt2_attention_decode_kv(out, q, k_cache, v_cache, block_table, table_stride, block_tokens, cu_seqlens, slot_ids, kv_lens,
+                                     rows, nh, nkv, d, d, scale, window, 0, max_splits, part_acc, part_ml, counters, stream);
 }

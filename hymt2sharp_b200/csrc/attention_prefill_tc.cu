@@ -22,7 +22,10 @@
 // Formulas: src/HyMT2Sharp/Ops.cs:359-455 (scores, kv head = head / group), :198-325 (softmax
 // over the visible keys), :535-595 (combine).  A query at position p sees keys
 // [max(0, p - window + 1), p].
-// Takes head sizes 64 and 128 and cache blocks of 64 tokens; other shapes stay with the general kernel.
+// Values may be of another width than keys (DV entries a head, O has DV columns), and the softmax may have a sink: one
+// more term in its denominator, of score 0 and without a value, added to a row's sum at the end.
+// Takes key and value sizes of 64 and 128 (in any pairing) and cache blocks of 64 tokens; other shapes stay with the
+// general kernel.
 #include "tc_common.cuh"
 
 namespace {
@@ -46,6 +49,7 @@ struct PrefillParams {
     int batch, qtiles, sm_count;
     float scale_log2;          // scale * log2(e)
     int* status;
+    int sink;
 };
 
 __device__ __forceinline__ float ex2_approx(float x) {
@@ -64,20 +68,20 @@ __device__ __forceinline__ void tmem_store16(uint32_t taddr, const float* v) {
 }
 
 
-template <int D>
+template <int D, int DV>
 __global__ void __launch_bounds__(NUM_THREADS, 2)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, PrefillParams p) {
-    constexpr int D_BOXES = D / 64;                         // TMA boxes of 64 elements along d
-    constexpr int Q_BYTES = Q_ROWS * D * 2, KV_TILE_BYTES = KEY_TILE * D * 2, P_BYTES = Q_ROWS * KEY_TILE * 2;
+    constexpr int D_BOXES = D / 64, DV_BOXES = DV / 64;     // TMA boxes of 64 elements along d and along dv
+    constexpr int Q_BYTES = Q_ROWS * D * 2, K_TILE_BYTES = KEY_TILE * D * 2, V_TILE_BYTES = KEY_TILE * DV * 2, P_BYTES = Q_ROWS * KEY_TILE * 2;
     // P of a tile (16 KB) takes the place of the tile's K (free once S is computed): a K slot holds the larger of the two
-    constexpr int K_SLOT_BYTES = KV_TILE_BYTES >= P_BYTES ? KV_TILE_BYTES : P_BYTES;
-    constexpr int BARS_OFFSET = Q_BYTES + K_SLOTS * K_SLOT_BYTES + KV_STAGES * KV_TILE_BYTES;
-    constexpr int TMEM_COLS = 256;                          // S of even tiles: columns [0, 64), of odd tiles [64, 128); O: [128, 128 + D)
+    constexpr int K_SLOT_BYTES = K_TILE_BYTES >= P_BYTES ? K_TILE_BYTES : P_BYTES;
+    constexpr int BARS_OFFSET = Q_BYTES + K_SLOTS * K_SLOT_BYTES + KV_STAGES * V_TILE_BYTES;
+    constexpr int TMEM_COLS = 256;                          // S of even tiles: columns [0, 64), of odd tiles [64, 128); O: [128, 128 + DV)
     constexpr uint32_t S_COL = 0, O_COL = 128;
-    // D float32, A and B bfloat16; S: both K-major, N = 64; O: B is MN-major, N = D
+    // D float32, A and B bfloat16; S: both K-major, N = 64; O: B is MN-major, N = DV
     constexpr uint32_t IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(KEY_TILE >> 3) << 17) | ((uint32_t)(Q_ROWS >> 4) << 24);
-    constexpr uint32_t IDESC_O = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(Q_ROWS >> 4) << 24);
+    constexpr uint32_t IDESC_O = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(DV >> 3) << 17) | ((uint32_t)(Q_ROWS >> 4) << 24);
 
     // No static shared memory: the dynamic part then starts on a 1 KB boundary, which the swizzled tiles need,
     // and two CTAs of 112 KB fit an SM.  Barriers and the two words lie behind the tiles.
@@ -112,7 +116,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     }
     const uint32_t q_smem = base, k_smem = q_smem + Q_BYTES, v_smem = k_smem + K_SLOTS * K_SLOT_BYTES;
     auto k_of = [&](int tile) { return k_smem + (tile % K_SLOTS) * K_SLOT_BYTES; };   // K of a tile, then its P
-    auto v_of = [&](int tile) { return v_smem + (tile % KV_STAGES) * KV_TILE_BYTES; };
+    auto v_of = [&](int tile) { return v_smem + (tile % KV_STAGES) * V_TILE_BYTES; };
     const uint32_t kv_full = smem_u32(&bars[0]), kv_empty = smem_u32(&bars[KV_STAGES]);
     const uint32_t q_full = smem_u32(&bars[2 * KV_STAGES]), o_full = q_full + 8;
     const uint32_t s_full = o_full + 8 * O_BARS, p_full = s_full + 8 * S_BUFFERS;   // s_full: one for even, one for odd tiles
@@ -151,7 +155,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         // ---- producer: Q with K(0), then K(i + 1) with V(i) ---------------------------------------
         const int* table = p.block_table + (size_t)slot * p.table_stride;
         auto cache_row = [&](int tile) { return (table[tile_begin + tile] * p.nkv + kvh) * KEY_TILE; };
-        mbar_expect_tx(q_full, Q_BYTES + KV_TILE_BYTES);
+        mbar_expect_tx(q_full, Q_BYTES + K_TILE_BYTES);
         for (int x = 0; x < D_BOXES; x++) {
             tma_load_2d(q_smem + x * (Q_ROWS * 128), &map_q, q_full, head * D + x * 64, tok0 + qtile * Q_ROWS);
             tma_load_2d(k_of(0) + x * (KEY_TILE * 128), &map_k, q_full, x * 64, cache_row(0));
@@ -162,13 +166,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             // P·V of tile i - 2 is through: V's slot is free, and so is the slot of K(i - 2), which takes K(i + 1)
             if (!mbar_wait(kv_empty + 8 * s, ((i / KV_STAGES) & 1) ^ 1, abort_flag, p.status, 111)) break;
             const bool more = i + 1 < num_tiles;
-            mbar_expect_tx(kv_full + 8 * s, (more ? 2 : 1) * KV_TILE_BYTES);
+            mbar_expect_tx(kv_full + 8 * s, (more ? K_TILE_BYTES : 0) + V_TILE_BYTES);
             const int v_row = cache_row(i), k_row = more ? cache_row(i + 1) : 0;
             const uint32_t k_dst = k_of(i + 1), v_dst = v_of(i);
-            for (int x = 0; x < D_BOXES; x++) {
+            for (int x = 0; x < D_BOXES; x++)
                 if (more) tma_load_2d(k_dst + x * (KEY_TILE * 128), &map_k, kv_full + 8 * s, x * 64, k_row);
-                tma_load_2d(v_dst + x * (KEY_TILE * 128), &map_v, kv_full + 8 * s, x * 64, v_row);
-            }
+            for (int x = 0; x < DV_BOXES; x++) tma_load_2d(v_dst + x * (KEY_TILE * 128), &map_v, kv_full + 8 * s, x * 64, v_row);
             issued = i + 1;
         }
         if (*abort_flag) {   // nothing may still be landing when the CTA leaves
@@ -216,7 +219,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     } else if (warp == 2 && lane == 0) {
         // ---- second MMA issuer: O += P V once the softmax warps have written P (and rescaled O where a maximum rose)
         const uint64_t p_desc0 = desc_k_major(k_smem), v_desc0 = desc_mn_major(v_smem, KEY_TILE * 128);
-        constexpr uint64_t K_STEP = K_SLOT_BYTES >> 4, V_STEP = KV_TILE_BYTES >> 4;
+        constexpr uint64_t K_STEP = K_SLOT_BYTES >> 4, V_STEP = V_TILE_BYTES >> 4;
         for (int i = 0; i < num_tiles; i++) {
             const int s = i % KV_STAGES;
             if (!mbar_wait(p_full + 8 * (i % P_BARS), (i / P_BARS) & 1, abort_flag, p.status, 114)) break;
@@ -271,7 +274,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 if (!(ok = mbar_wait(o_full + 8 * ((i - 1) % O_BARS), ((i - 1) / O_BARS) & 1, abort_flag, p.status, 116))) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-                for (int c = 0; c < D; c += 16) {   // 16 columns at a time: the row's 64 scores are live in registers
+                for (int c = 0; c < DV; c += 16) {   // 16 columns at a time: the row's 64 scores are live in registers
                     float o[16];
                     tmem_load16(lane_addr + O_COL + c, o);
 #pragma unroll
@@ -310,7 +313,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 !(ok = mbar_wait(kv_full + 8 * (i % KV_STAGES), (i / KV_STAGES) & 1, abort_flag, p.status, 110))) break;
             if (r < KEY_TILE && key0 + r >= kv_len) {
 #pragma unroll
-                for (int x = 0; x < D_BOXES; x++) {
+                for (int x = 0; x < DV_BOXES; x++) {
                     const uint32_t rowp = v_of(i) + x * (KEY_TILE * 128) + r * 128;
 #pragma unroll
                     for (int c = 0; c < 8; c++)
@@ -324,10 +327,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (ok) ok = mbar_wait(o_full + 8 * ((num_tiles - 1) % O_BARS), ((num_tiles - 1) / O_BARS) & 1, abort_flag, p.status, 117);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (ok) {
+            // the sink: a term exp2(0 - m) in the sum (m is the offset that every numerator of the row was taken against; a row
+            // that sees a key has a finite one)
+            if (p.sink && m > -INFINITY) l += exp2f(-m);
             const float inv = l > 0.f ? 1.0f / l : 0.f;
-            __nv_bfloat16* dst = p.out + ((size_t)(tok0 + qtile * Q_ROWS + r) * p.nh + head) * D;
+            __nv_bfloat16* dst = p.out + ((size_t)(tok0 + qtile * Q_ROWS + r) * p.nh + head) * DV;
 #pragma unroll
-            for (int c = 0; c < D; c += 32) {
+            for (int c = 0; c < DV; c += 32) {
                 float o[32];
                 tmem_load32(lane_addr + O_COL + c, o);   // all lanes of the warp take part in the load
                 if (row_ok) {
@@ -351,13 +357,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     }
 }
 
-template <int D>
+template <int D, int DV>
 int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const PrefillParams& p, dim3 grid,
            cudaStream_t stream) {
-    constexpr size_t kv_tile = KEY_TILE * D * 2, p_tile = Q_ROWS * KEY_TILE * 2;
-    constexpr size_t smem = Q_ROWS * D * 2 + K_SLOTS * (kv_tile >= p_tile ? kv_tile : p_tile) + KV_STAGES * kv_tile +
+    constexpr size_t k_tile = KEY_TILE * D * 2, v_tile = KEY_TILE * DV * 2, p_tile = Q_ROWS * KEY_TILE * 2;
+    constexpr size_t smem = Q_ROWS * D * 2 + K_SLOTS * (k_tile >= p_tile ? k_tile : p_tile) + KV_STAGES * v_tile +
                             NUM_BARS * 8 + 8;   // tiles, barriers, two words
-    auto kernel = attention_prefill_tc_kernel<D>;
+    auto kernel = attention_prefill_tc_kernel<D, DV>;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -379,14 +385,14 @@ HYMT2_API int hymt2_attention_prefill_tc_protocol(int* out) {
     return HYMT2_OK;
 }
 
-// out, q: [tokens, nh * d] bfloat16; k_cache, v_cache: one layer's planes [blocks][nkv][64][d] bfloat16.
-HYMT2_API int hymt2_attention_prefill_tc(void* out, const void* q, const void* k_cache, const void* v_cache,
-                                         long cache_blocks, const int* block_table, int table_stride, int block_tokens,
-                                         const int* cu_seqlens, const int* slot_ids, const int* kv_lens, int batch,
-                                         int tokens, int max_new_tokens, int nh, int nkv, int d, float scale, int window,
-                                         int* status, cudaStream_t stream) {
+// out: [tokens, nh * dv], q: [tokens, nh * d] bfloat16; k_cache [blocks][nkv][64][d], v_cache [blocks][nkv][64][dv]: one layer's planes.
+HYMT2_API int hymt2_attention_prefill_tc_kv(void* out, const void* q, const void* k_cache, const void* v_cache,
+                                            long cache_blocks, const int* block_table, int table_stride, int block_tokens,
+                                            const int* cu_seqlens, const int* slot_ids, const int* kv_lens, int batch,
+                                            int tokens, int max_new_tokens, int nh, int nkv, int d, int dv, float scale, int window,
+                                            int sink, int* status, cudaStream_t stream) {
     if (tokens == 0 || batch == 0) return HYMT2_OK;
-    HYMT2_REQUIRE(d == 64 || d == 128, "attention_prefill_tc: head_dim %d is not taken (64 and 128 are)", d);
+    HYMT2_REQUIRE((d == 64 || d == 128) && (dv == 64 || dv == 128), "attention_prefill_tc: heads of %d and %d are not taken (64 and 128 are)", d, dv);
     HYMT2_REQUIRE(block_tokens == KEY_TILE, "attention_prefill_tc: cache blocks must hold %d tokens", KEY_TILE);
     HYMT2_REQUIRE(nh > 0 && nkv > 0 && nh % nkv == 0 && batch <= 65535 && nh <= 65535, "attention_prefill_tc: bad sizes");
     HYMT2_REQUIRE(((uintptr_t)q % 16 == 0) && ((uintptr_t)k_cache % 16 == 0) && ((uintptr_t)v_cache % 16 == 0) &&
@@ -395,7 +401,7 @@ HYMT2_API int hymt2_attention_prefill_tc(void* out, const void* q, const void* k
     CUtensorMap mq, mk, mv;
     const long cache_rows = cache_blocks * nkv * KEY_TILE;
     const bool ok = make_map(&mq, q, tokens, (long)nh * d, (long)nh * d, Q_ROWS) &&
-                    make_map(&mk, k_cache, cache_rows, d, d, KEY_TILE) && make_map(&mv, v_cache, cache_rows, d, d, KEY_TILE);
+                    make_map(&mk, k_cache, cache_rows, d, d, KEY_TILE) && make_map(&mv, v_cache, cache_rows, dv, dv, KEY_TILE);
     HYMT2_REQUIRE(ok, "attention_prefill_tc: cuTensorMapEncodeTiled refused the operands");
     const int qtiles = (max_new_tokens + Q_ROWS - 1) / Q_ROWS;
     HYMT2_REQUIRE((long)qtiles * nh * batch <= 2147483647L, "attention_prefill_tc: too many tiles");
@@ -403,7 +409,18 @@ HYMT2_API int hymt2_attention_prefill_tc(void* out, const void* q, const void* k
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     PrefillParams p{(__nv_bfloat16*)out, block_table, cu_seqlens, slot_ids, kv_lens, table_stride, nh, nkv, window,
-                    batch, qtiles, sms, scale * 1.4426950408889634f, status};
+                    batch, qtiles, sms, scale * 1.4426950408889634f, status, sink};
     dim3 grid((unsigned)(qtiles * nh * batch), 1, 1);
-    return d == 128 ? launch<128>(mq, mk, mv, p, grid, stream) : launch<64>(mq, mk, mv, p, grid, stream);
+    if (d == 128) return dv == 128 ? launch<128, 128>(mq, mk, mv, p, grid, stream) : launch<128, 64>(mq, mk, mv, p, grid, stream);
+    return dv == 128 ? launch<64, 128>(mq, mk, mv, p, grid, stream) : launch<64, 64>(mq, mk, mv, p, grid, stream);
+}
+
+// The classic form: values as wide as keys, no sink.
+HYMT2_API int hymt2_attention_prefill_tc(void* out, const void* q, const void* k_cache, const void* v_cache,
+                                         long cache_blocks, const int* block_table, int table_stride, int block_tokens,
+                                         const int* cu_seqlens, const int* slot_ids, const int* kv_lens, int batch,
+                                         int tokens, int max_new_tokens, int nh, int nkv, int d, float scale, int window,
+                                         int* status, cudaStream_t stream) {
+    return hymt2_attention_prefill_tc_kv(out, q, k_cache, v_cache, cache_blocks, block_table, table_stride, block_tokens, cu_seqlens,
+                                         slot_ids, kv_lens, batch, tokens, max_new_tokens, nh, nkv, d, d, scale, window, 0, status, stream);
 }

@@ -102,6 +102,22 @@ def try_attention(out, q, k_plane, v_plane, block_table, ctx, nh, nkv, d, scale,
 
 
 def try_attention_kv(out, q, k_plane, v_plane, block_table, ctx, nh, nkv, d, dv, scale, window, sink) -> bool:
-    """The attention with values of their own width and an optional sink on the tensor cores, where a kernel takes the
-    shape; False: the caller runs the general kernel."""
+    """The attention with values of their own width and an optional sink, in bfloat16 with keys and values of 64 or 128
+    entries a head: decode steps go to the streaming decode kernel, steps with longer pieces to the tcgen05 flash-attention
+    kernel (cache blocks of 64 tokens).  False: the caller runs the general kernel."""
+    bt = k_plane.shape[2]
+    if out.dtype != torch.bfloat16 or d not in (64, 128) or dv not in (64, 128) or bt & (bt - 1):
+        return False
+    if ctx.decode:
+        splits = max(1, -(-ctx.max_kv_len // DECODE_CHUNK_KEYS))
+        na, nm = ops.attention_simt_scratch(ctx.num_tokens, nh, dv, splits)
+        acc = torch.empty(na, dtype=torch.float32, device=out.device)
+        ml = torch.empty(nm, dtype=torch.float32, device=out.device)
+        ops.attention_decode_kv(out, q, k_plane, v_plane, block_table, ctx.cu_seqlens, ctx.slot_ids, ctx.kv_lens, nh, nkv, d, dv, scale,
+                                window, sink, splits, acc, ml, ops.zeroed_counters(out.device, ctx.num_tokens * nh))
+        return True
+    if bt == 64:
+        ops.attention_prefill_tc_kv(out, q, k_plane, v_plane, block_table, ctx.cu_seqlens, ctx.slot_ids, ctx.kv_lens, ctx.num_seqs,
+                                    ctx.max_new_tokens, nh, nkv, d, dv, scale, window, sink, ops.device_status(out.device))
+        return True
     return False

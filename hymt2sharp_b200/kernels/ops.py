@@ -1289,3 +1289,49 @@ def moe_combine(out: torch.Tensor, y: torch.Tensor, x: torch.Tensor, pair_row: t
         raise KernelError(f"moe_combine: shapes out {tuple(out.shape)} y {tuple(y.shape)} x {tuple(x.shape)} pairs {tuple(pair_row.shape)}")
     _check(_lib().hymt2_moe_combine(_ptr(out), _ptr(y), _ptr(x), c_int(dtype_code(x.dtype)), _ptr(pair_row), _ptr(weight), c_int(T), c_int(H),
                                     c_int(pair_row.shape[1]), c_int(1 if add else 0), _stream()), "moe_combine")
+
+
+def _attention_kv_shapes(what: str, out, q, k_plane, v_plane, nh, nkv, d, dv) -> None:
+    _need(out, "out", torch.bfloat16, 2); _need(q, "q", torch.bfloat16, 2)
+    _need(k_plane, "k_plane", torch.bfloat16, 4); _need(v_plane, "v_plane", torch.bfloat16, 4)
+    if out.shape[1] != nh * dv or q.shape[1] != nh * d or q.shape[0] < out.shape[0] or k_plane.shape[1] != nkv or k_plane.shape[3] != d \
+            or v_plane.shape != (*k_plane.shape[:3], dv):
+        raise KernelError(f"{what}: shapes out {tuple(out.shape)} q {tuple(q.shape)} k {tuple(k_plane.shape)} v {tuple(v_plane.shape)}")
+
+
+def attention_prefill_tc_kv(out: torch.Tensor, q: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tensor, block_table: torch.Tensor,
+                            cu_seqlens: torch.Tensor, slot_ids: torch.Tensor, kv_lens: torch.Tensor, batch: int, max_new_tokens: int,
+                            nh: int, nkv: int, d: int, dv: int, scale: float, window: int, sink: bool, status: torch.Tensor) -> None:
+    """attention_prefill_tc with keys of d and values of dv entries a head (64 or 128 each; out [T, nh * dv]) and optionally a
+    sink in the softmax."""
+    _attention_kv_shapes("attention_prefill_tc", out, q, k_plane, v_plane, nh, nkv, d, dv)
+    _need(block_table, "block_table", torch.int32, 2)
+    for t, n in ((cu_seqlens, "cu_seqlens"), (slot_ids, "slot_ids"), (kv_lens, "kv_lens")):
+        _need(t, n, torch.int32, 1)
+    _check(_lib().hymt2_attention_prefill_tc_kv(_ptr(out), _ptr(q), _ptr(k_plane), _ptr(v_plane), c_long(k_plane.shape[0]),
+                                                _ptr(block_table), c_int(block_table.stride(0)), c_int(k_plane.shape[2]),
+                                                _ptr(cu_seqlens), _ptr(slot_ids), _ptr(kv_lens), c_int(batch), c_int(out.shape[0]),
+                                                c_int(max_new_tokens), c_int(nh), c_int(nkv), c_int(d), c_int(dv), c_float(scale),
+                                                c_int(window), c_int(1 if sink else 0), _ptr(status), _stream()), "attention_prefill_tc")
+
+
+def attention_decode_kv(out: torch.Tensor, q: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tensor, block_table: torch.Tensor,
+                        cu_seqlens: torch.Tensor, slot_ids: torch.Tensor, kv_lens: torch.Tensor, nh: int, nkv: int, d: int, dv: int,
+                        scale: float, window: int, sink: bool, max_splits: int, part_acc: torch.Tensor, part_ml: torch.Tensor,
+                        counters: torch.Tensor) -> None:
+    """attention_decode with keys of d and values of dv entries a head (64 or 128 each) and optionally a sink; the scratch is
+    sized as attention_simt_scratch with dv."""
+    _attention_kv_shapes("attention_decode", out, q, k_plane, v_plane, nh, nkv, d, dv)
+    rows = out.shape[0]
+    _need(block_table, "block_table", torch.int32, 2)
+    for t, n in ((cu_seqlens, "cu_seqlens"), (slot_ids, "slot_ids"), (kv_lens, "kv_lens")):
+        _need(t, n, torch.int32, 1)
+    need_acc, need_ml = attention_simt_scratch(rows, nh, dv, max_splits)
+    _need(part_acc, "part_acc", torch.float32); _need(part_ml, "part_ml", torch.float32); _need(counters, "counters", torch.int32, 1)
+    if part_acc.numel() < need_acc or part_ml.numel() < need_ml or counters.numel() < rows * nh:
+        raise KernelError("attention_decode: the scratch for the partials is too small")
+    _check(_lib().hymt2_attention_decode_kv(_ptr(out), _ptr(q), _ptr(k_plane), _ptr(v_plane), _ptr(block_table),
+                                            c_int(block_table.stride(0)), c_int(k_plane.shape[2]), _ptr(cu_seqlens), _ptr(slot_ids),
+                                            _ptr(kv_lens), c_int(rows), c_int(nh), c_int(nkv), c_int(d), c_int(dv), c_float(scale),
+                                            c_int(window), c_int(1 if sink else 0), c_int(max_splits), _ptr(part_acc), _ptr(part_ml),
+                                            _ptr(counters), _stream()), "attention_decode")

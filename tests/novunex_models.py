@@ -66,11 +66,11 @@ def make_model_dir(folder: str, name: str) -> str:
         if k.endswith(".mlp.router"):
             tensors[k] = (tensors[k].float() * ROUTER_SPREAD).to(tensors[k].dtype)
         if k.endswith(".mlp.correction") and spec.get("spaced_corrections"):
-            # corrections half a score apart, in a shuffled order: two outputs tie for the last place only where their scores
-            # differ by a multiple of 0.5, so the bfloat16 engine and the plain model nearly always choose alike, while an
-            # output whose score passes one half still overtakes its neighbour
+            # corrections a whole score apart, in a shuffled order: scores lie between 0 and 1, so the corrections alone decide
+            # the choice and the bfloat16 engine chooses as the plain model does; the weights are still the tokens' own scores.
+            # (The other model keeps random corrections, and with them a choice that differs from token to token.)
             n = tensors[k].shape[0]
             order = torch.randperm(n, generator=torch.Generator().manual_seed(n + spec["seed"]))
-            tensors[k] = (0.5 * order.float()).to(tensors[k].dtype)
+            tensors[k] = order.float().to(tensors[k].dtype)
     save_file(tensors, path)
     return folder

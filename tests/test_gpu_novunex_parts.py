@@ -69,7 +69,11 @@ SCALED = dict(factor=4.0, low=1.0, high=4.0, original=64)
     ("attention_2", 40, 4, 2, 6, 9, 6, SCALED),         # values wider than keys, the whole head rotated, scaled frequencies
     ("attention", 64, 4, 4, 16, 16, 0, None),           # no rotation at all, as many kv heads as heads
     ("attention_2", 96, 8, 2, 64, 32, 64, SCALED),
-    ("attention", 128, 4, 2, 128, 64, 32, None),
+    ("attention", 128, 4, 2, 128, 64, 32, None),         # from here on the bfloat16 engine runs its tensor-core prompt kernel and
+    ("attention_2", 128, 8, 2, 64, 64, 64, SCALED),      # its streaming decode kernel: keys and values of 64 and 128 in every pairing,
+    ("attention", 64, 2, 1, 64, 128, 16, None),          # with and without the sink
+    ("attention_2", 128, 4, 4, 128, 128, 128, None),
+    ("attention", 128, 12, 2, 128, 128, 64, None),       # six heads on a kv head
 ])
 def test_attention_forms_in_prompts_portions_and_decoding(dtype, kind, hidden, heads, kv, d, dv, dims, scaling):
     torch.manual_seed(hidden + d)
@@ -128,7 +132,7 @@ def _planted(dtype, sink, d, dv, nkv, g, length, key_at, decode_from=None, secon
     """Keys of small random entries except ONE, which is the query's direction made long: the row's output must be that
     key's value (less the sink's share).  Written into the cache through the appending kernel, read by the attention."""
     from hymt2sharp_b200.cache import GroupSpec, PagedCache
-    from hymt2sharp_b200.kernels import ops
+    from hymt2sharp_b200.kernels import fast, ops
     torch.manual_seed(key_at + length)
     nh = nkv * g
     cache = PagedCache([GroupSpec("full", nkv, d, 1, 0, 2, 0 if dv == d else dv)], dtype, DEV, 4096, max_slots=4)
@@ -160,8 +164,10 @@ def _planted(dtype, sink, d, dv, nkv, g, length, key_at, decode_from=None, secon
             split, ms = 256, -(-ctx.max_kv_len // 256)
             na, nm = ops.attention_simt_scratch(T, nh, dv, ms)
             acc, ml = torch.empty(na, device=DEV), torch.empty(nm, device=DEV)
-        ops.attention_simt_kv(out, q, k_plane, v_plane, cache.tables[0], ctx.cu_seqlens, ctx.slot_ids, ctx.kv_lens, ctx.num_seqs,
-                              ctx.max_new_tokens, nh, nkv, d, dv, 1.0, 0, sink, split, ms, acc, ml)
+        # the engine's own choice of kernels: tensor cores where they take the shape, else the general kernel
+        if not fast.try_attention_kv(out, q, k_plane, v_plane, cache.tables[0], ctx, nh, nkv, d, dv, 1.0, 0, sink):
+            ops.attention_simt_kv(out, q, k_plane, v_plane, cache.tables[0], ctx.cu_seqlens, ctx.slot_ids, ctx.kv_lens, ctx.num_seqs,
+                                  ctx.max_new_tokens, nh, nkv, d, dv, 1.0, 0, sink, split, ms, acc, ml)
         cache.end_step(plan)
         o = 0
         for i in idx:
@@ -173,13 +179,15 @@ def _planted(dtype, sink, d, dv, nkv, g, length, key_at, decode_from=None, secon
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("sink", [False, True])
-@pytest.mark.parametrize("key_at", [0, 1, 63, 64, 255, 256, 319, 320, 511])
-def test_one_far_key_is_found_in_prompts_and_in_decoding(dtype, sink, key_at):
-    """The key stands at the first token, at both sides of a block's end (64 tokens) and of a chunk's end (256 keys in
-    decoding), and hundreds of tokens back, beside a second, shorter sequence in the same batch."""
+@pytest.mark.parametrize("d, dv", [(16, 24), (128, 64)])
+@pytest.mark.parametrize("key_at", [0, 1, 63, 64, 127, 128, 255, 256, 319, 320, 511])
+def test_one_far_key_is_found_in_prompts_and_in_decoding(dtype, sink, key_at, d, dv):
+    """The key stands at the first token, at both sides of a block's end (64 tokens), of a query tile's end (128 rows of the
+    tensor-core kernel) and of a chunk's end (256 keys in decoding), and hundreds of tokens back, beside a second, shorter
+    sequence in the same batch.  Heads of 16 and 24 run the general kernels; heads of 128 and 64 the fast ones in bfloat16."""
     length = 600
     for decode_from in (None, 590):
-        outs, vs = _planted(dtype, sink, 16, 24, 2, 2, length, key_at, decode_from, second=70)
+        outs, vs = _planted(dtype, sink, d, dv, 2, 2, length, key_at, decode_from, second=70)
         for t in (length - 1, length - 5):
             got = outs[(0, t)]
             want = vs[0][key_at][:, None, :].expand_as(got)
