@@ -140,7 +140,7 @@ def reference_arm() -> int:
     return 0
 
 
-# ---- another design beside the flagship: `--design pemezen` -----------------------------------------------------------------
+# ---- another design beside the flagship: `--design pemezen`, `--design novunex` ------------------------------------------------
 # Sizes that resemble a real model's layers (random weights), and a Hunyuan-dense model of the same width, depth and
 # nearly the same number of weights per layer beside it: the closest model that the library has.
 DESIGN_SIZES = {
@@ -150,16 +150,44 @@ DESIGN_SIZES = {
               dense=dict(num_attention_heads=16, num_key_value_heads=4, intermediate_size=5632)),
 }
 DESIGN_ORDER = ["latent_attention_2", "latent_attention", "rglru", "latent_attention_2"]   # repeated up to --layers
+# Novunex: heads of 128 with values of 64; of every four layers the second reads the first one's keys and values; a mixture of
+# `experts` experts of width `ff` plus `identity` identity experts, `top` chosen, and a shared expert: 4 x ff + shared inner
+# width is at work for a token, close to the dense model's feed-forward
+NOVUNEX_SIZES = {
+    "s": dict(width=1024, vocab=32768, heads=8, kv_heads=2, dim=128, vdim=64, experts=16, identity=2, top=4, ff=512, shared=1024,
+              dense=DESIGN_SIZES["s"]["dense"]),
+    "m": dict(width=2048, vocab=65536, heads=16, kv_heads=4, dim=128, vdim=64, experts=32, identity=2, top=4, ff=1024, shared=2048,
+              dense=DESIGN_SIZES["m"]["dense"]),
+}
+NOVUNEX_ORDER = ["attention_2", "attention_2 kv_from", "attention", "attention"]   # repeated up to --layers
 
 
-def make_design_models(size: str, layers: int) -> dict:
-    """Model folders with random weights: {"pemezen": ..., "hunyuan_dense": ...}."""
-    from hymt2sharp_b200.config import HunyuanDenseConfig, PemezenConfig
-    from hymt2sharp_b200.weights import write_random_model
-    z = DESIGN_SIZES[size]
-    rot = dict(dims=z["rot_dim"], base=10000.0, scaling=dict(factor=8.0, original=1024, fast=32.0, slow=1.0))
+def novunex_config(size: str, layers: int):
+    from hymt2sharp_b200.config import NovunexConfig
+    z = NOVUNEX_SIZES[size]
     entries = []
     for i in range(layers):
+        kind = NOVUNEX_ORDER[i % len(NOVUNEX_ORDER)]
+        second = kind.startswith("attention_2")
+        rot = dict(dims=z["dim"], base=500000.0, scaling=dict(factor=8.0, low=1.0, high=4.0, original=8192)) if second \
+            else dict(dims=z["dim"] // 2, base=10000.0)
+        mixer = dict(heads=z["heads"], kv_heads=z["kv_heads"], dim=z["dim"], vdim=z["vdim"], scale=z["dim"] ** -0.5, rot=rot)
+        if kind.endswith("kv_from"):
+            mixer["kv_from"] = i - 1
+        mlp = dict(kind="moe", expert=dict(ff=z["ff"]), router=dict(experts=z["experts"], identity=z["identity"], top=z["top"]),
+                   shared=dict(ff=z["shared"]))
+        entries.append(dict(type=kind.split()[0], mixer=mixer, mlp=mlp))
+    return NovunexConfig.from_dict(dict(architecture="Novunex", vocab=z["vocab"], width=z["width"], layers=entries, norm=dict(eps=1e-6)))
+
+
+def make_design_models(size: str, layers: int, design: str = "pemezen") -> dict:
+    """Model folders with random weights: {the design: ..., "hunyuan_dense": ...}."""
+    from hymt2sharp_b200.config import HunyuanDenseConfig, PemezenConfig
+    from hymt2sharp_b200.weights import write_random_model
+    z = (NOVUNEX_SIZES if design == "novunex" else DESIGN_SIZES)[size]
+    rot = dict(dims=z.get("rot_dim"), base=10000.0, scaling=dict(factor=8.0, original=1024, fast=32.0, slow=1.0))
+    entries = []
+    for i in range(layers if design == "pemezen" else 0):
         kind = DESIGN_ORDER[i % len(DESIGN_ORDER)]
         if kind == "rglru":
             mixer = dict(width=z["rec_width"], blocks=z["rec_blocks"], conv=4)
@@ -167,20 +195,23 @@ def make_design_models(size: str, layers: int) -> dict:
             mixer = dict(heads=z["heads"], dim=z["dim"], rot_dim=z["rot_dim"], vdim=z["vdim"], kv_rank=z["kv_rank"],
                          scale=(z["dim"] + z["rot_dim"]) ** -0.5, rot=rot)
         entries.append(dict(type=kind, mixer=mixer, mlp=dict(kind="dense", ff=z["ff"])))
-    new = PemezenConfig.from_dict(dict(architecture="Pemezen", vocab=z["vocab"], width=z["width"], layers=entries,
-                                       norm=dict(eps=1e-6, groups=2), canon=dict(taps=4), embedding=dict(scale=1.0), logit_softcap=30.0))
+    if design == "novunex":
+        new = novunex_config(size, layers)
+    else:
+        new = PemezenConfig.from_dict(dict(architecture="Pemezen", vocab=z["vocab"], width=z["width"], layers=entries,
+                                           norm=dict(eps=1e-6, groups=2), canon=dict(taps=4), embedding=dict(scale=1.0), logit_softcap=30.0))
     old = HunyuanDenseConfig.from_dict(dict(COMMON, architectures=["HunYuanDenseV1ForCausalLM"], num_hidden_layers=layers,
                                             hidden_size=z["width"], vocab_size=z["vocab"], tie_word_embeddings=False,
                                             rope_scaling={"type": "dynamic", "alpha": 1000.0}, **z["dense"]))
     old_data = {k: v for k, v in old.to_dict().items()}
     folders = {}
-    for name, cfg in (("pemezen", new), ("hunyuan_dense", HunyuanDenseConfig.from_dict(old_data))):
+    for name, cfg in ((design, new), ("hunyuan_dense", HunyuanDenseConfig.from_dict(old_data))):
         folders[name] = write_random_model(tempfile.mkdtemp(prefix=f"hymt2_bench_{name}_"), cfg, 7, 0.02)
     return folders
 
 
 def design_bench(args) -> int:
-    """Prefill and decode throughput of the Pemezen design beside the Hunyuan-dense model of equal size, with each phase's
+    """Prefill and decode throughput of another design (--design) beside the Hunyuan-dense model of equal size, with each phase's
     kernels timed one by one (CUDA events between launches; a captured decode step is stamped by the device's clock)."""
     import numpy as np
     import torch
@@ -191,14 +222,14 @@ def design_bench(args) -> int:
     from hymt2sharp_b200.sampling import BatchSampler, GREEDY
 
     pk, pk_source = peaks()
-    z = DESIGN_SIZES[args.design_size]
+    z = (NOVUNEX_SIZES if args.design == "novunex" else DESIGN_SIZES)[args.design_size]
     layers = args.layers or 8
     batch, context, steps, warmup = args.batch or 8, args.prefill, max(1, args.decode or args.steps or 32), max(3, args.warmup)
     dtype = {"bf16": "bfloat16", "fp32": "float32"}[args.dtype]
     ev = lambda: torch.cuda.Event(enable_timing=True)
     rng = np.random.default_rng(99)
-    folders = make_design_models(args.design_size, layers)
-    out = {"design": "pemezen", "size": args.design_size, "layers": layers, "dtype": args.dtype, "data": "synthetic (random weights, random token ids)",
+    folders = make_design_models(args.design_size, layers, args.design)
+    out = {"design": args.design, "size": args.design_size, "layers": layers, "dtype": args.dtype, "data": "synthetic (random weights, random token ids)",
            "sizes": {k: v for k, v in z.items() if k != "dense"}, "closest": dict(z["dense"], hidden_size=z["width"], head_dim=COMMON["head_dim"]),
            "prefill_tokens": context, "decode": {"batch": batch, "context": context, "steps": steps}, "peaks": pk_source, "models": {}}
     launches0 = ops.launches
@@ -392,7 +423,7 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--no-kernels", action="store_true", help="skip the kernels timed alone")
     ap.add_argument("--no-graph", action="store_true")
-    ap.add_argument("--design", default=None, choices=["pemezen"],
+    ap.add_argument("--design", default=None, choices=["pemezen", "novunex"],
                     help="instead of the flagship workload: prefill (--prefill tokens) and decode (--batch sequences of --prefill tokens, "
                          "--steps steps) of this design beside the Hunyuan-dense model of equal size, with per-kernel times")
     ap.add_argument("--design-size", default="s", choices=sorted(DESIGN_SIZES))

@@ -263,6 +263,71 @@ gemm_skinny_batched_kernel(TC* __restrict__ C, const T* __restrict__ A, const T*
     }
 }
 
+// The grouped product for few sorted rows (a decode step): row tiles of GROUP_SKINNY_ROWS rows, a warp per output column
+// reads its weight row once, 16 bytes a lane, and keeps a float32 sum for every row of the tile.  The time is that of
+// reading the matrices of the groups in use once.
+constexpr int GROUP_SKINNY_ROWS = 8;
+
+template <typename T, typename TC, int EPI>
+__global__ void __launch_bounds__(SKINNY_WARPS * 32)
+gemm_skinny_grouped_kernel(TC* __restrict__ C, const T* __restrict__ A, const T* __restrict__ W, const int* __restrict__ tile_group,
+                           const int* __restrict__ row_source, int gather, int N, int K, long lda, long ldc, long w_gs, bool vec) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int group = tile_group[blockIdx.y];
+    if (group < 0) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n = blockIdx.x * SKINNY_WARPS + warp;
+    if (n >= N) return;
+    const int m0 = blockIdx.y * GROUP_SKINNY_ROWS;
+    const T* a_row[GROUP_SKINNY_ROWS];
+    bool ok[GROUP_SKINNY_ROWS];
+#pragma unroll
+    for (int m = 0; m < GROUP_SKINNY_ROWS; m++) {
+        const int src = row_source[m0 + m];
+        ok[m] = src >= 0;
+        a_row[m] = A + (size_t)(ok[m] ? (gather ? src : m0 + m) : 0) * lda;
+    }
+    const T* w = W + (size_t)group * w_gs + (size_t)n * K;
+    float acc[GROUP_SKINNY_ROWS];
+#pragma unroll
+    for (int m = 0; m < GROUP_SKINNY_ROWS; m++) acc[m] = 0.f;
+    constexpr int V = 16 / sizeof(T);
+    if (vec) {
+        for (int k = lane * V; k < K; k += 32 * V) {
+            float wv[V];
+            const uint4 raw = *reinterpret_cast<const uint4*>(w + k);
+            const T* wt = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+            for (int i = 0; i < V; i++) wv[i] = to_float(wt[i]);
+#pragma unroll
+            for (int m = 0; m < GROUP_SKINNY_ROWS; m++) {
+                if (ok[m]) {
+                    const uint4 ra = *reinterpret_cast<const uint4*>(a_row[m] + k);
+                    const T* at = reinterpret_cast<const T*>(&ra);
+#pragma unroll
+                    for (int i = 0; i < V; i++) acc[m] = fmaf(to_float(at[i]), wv[i], acc[m]);
+                }
+            }
+        }
+    } else {
+        for (int k = lane; k < K; k += 32) {
+            const float wv = to_float(w[k]);
+#pragma unroll
+            for (int m = 0; m < GROUP_SKINNY_ROWS; m++)
+                if (ok[m]) acc[m] = fmaf(to_float(a_row[m][k]), wv, acc[m]);
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < GROUP_SKINNY_ROWS; m++) {
+        if (ok[m]) {
+            float v = warp_sum(acc[m]);
+            if constexpr (EPI == EPI_RELU_SQUARED) { v = fmaxf(v, 0.f); v = v * v; }
+            if (lane == 0) C[(size_t)(m0 + m) * ldc + n] = from_float<TC>(v);
+        }
+    }
+}
+
 }  // namespace
 
 // C[M,N] (ldc) = epilogue(A[M,K] (lda) · W[N,K]^T (ldw)); for the swiglu epilogue W has 2N rows.
@@ -335,3 +400,29 @@ HYMT2_API int hymt2_gemm_simt_grouped(void* C, int c_dtype, const void* A, int a
 }
 
 HYMT2_API int hymt2_gemm_simt_group_tile() { return BM; }
+
+// The grouped product for few rows: row tiles of hymt2_gemm_skinny_group_tile() sorted rows, A and W of one type.
+HYMT2_API int hymt2_gemm_skinny_grouped(void* C, int c_dtype, const void* A, const void* W, int dtype, const int* tile_group,
+                                        const int* row_source, int gather, int tiles, int N, int K, long lda, long ldc, long w_gs,
+                                        int epilogue, cudaStream_t stream) {
+    if (tiles == 0 || N == 0) return HYMT2_OK;
+    HYMT2_REQUIRE(tiles > 0 && tiles <= 65535 && N > 0 && K > 0, "gemm_skinny_grouped: bad sizes tiles=%d N=%d K=%d", tiles, N, K);
+    HYMT2_REQUIRE(epilogue == EPI_STORE || epilogue == EPI_RELU_SQUARED, "gemm_skinny_grouped: unknown epilogue %d", epilogue);
+    HYMT2_REQUIRE(lda >= K && ldc >= N && tile_group && row_source, "gemm_skinny_grouped: bad arguments");
+    const dim3 grid((N + SKINNY_WARPS - 1) / SKINNY_WARPS, tiles);
+    HYMT2_DISPATCH_DTYPE(dtype, T, {
+        const long v = 16 / sizeof(T);
+        const bool vec = K % v == 0 && lda % v == 0 && w_gs % v == 0 && (uintptr_t)A % 16 == 0 && (uintptr_t)W % 16 == 0;
+        HYMT2_DISPATCH_DTYPE(c_dtype, TC, {
+            if (epilogue == EPI_STORE)
+                launch_pdl(gemm_skinny_grouped_kernel<T, TC, EPI_STORE>, grid, dim3(SKINNY_WARPS * 32), 0, stream, (TC*)C, (const T*)A,
+                           (const T*)W, tile_group, row_source, gather, N, K, lda, ldc, w_gs, vec);
+            else
+                launch_pdl(gemm_skinny_grouped_kernel<T, TC, EPI_RELU_SQUARED>, grid, dim3(SKINNY_WARPS * 32), 0, stream, (TC*)C,
+                           (const T*)A, (const T*)W, tile_group, row_source, gather, N, K, lda, ldc, w_gs, vec);
+        });
+    });
+    return hymt2_check_launch("gemm_skinny_grouped");
+}
+
+HYMT2_API int hymt2_gemm_skinny_group_tile() { return GROUP_SKINNY_ROWS; }

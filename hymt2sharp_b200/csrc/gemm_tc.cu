@@ -125,6 +125,12 @@ struct GemmTcParams {
     int withhold_block;      // -1; the debug entry names a k block whose copies the producer does NOT issue
     NormSide norm;
     int together = 0;        // splits through the workspace: every CTA of a tile folds a share of its columns (all of them are resident)
+    // A grouped product (persistent kernel only): the token rows are sorted by the weight matrix they meet, in segments of
+    // whole row tiles; tile_group[row tile] names the matrix (its rows start at group * group_rows of the weight map; a tile
+    // that is not in use says -1 and is computed against matrix 0, nobody reads its rows).  N is one matrix's rows.
+    const int* tile_group = nullptr;
+    long group_rows = 0;
+    int act = 0;             // store epilogue: 1 = the square of relu on the way out
 };
 
 // The copies of one stage (activations, weights, and for a split weight tile its second half) with, in front of them, a
@@ -924,8 +930,14 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
         // were issued (the stages of the first round are free anyway).
         uint32_t s = 0, round = 0;
         bool first = true, looked = true;
+        if (p.tile_group) pdl_wait();   // which weights a tile meets was written by the kernel before
         for (int tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x) {
-            const int a_row0 = (tile % tiles_m) * TILE_M, b_row0 = (tile / tiles_m) * OUT_COLS;
+            const int a_row0 = (tile % tiles_m) * TILE_M;
+            int b_row0 = (tile / tiles_m) * OUT_COLS;
+            if (p.tile_group) {
+                const int group = p.tile_group[tile % tiles_m];
+                b_row0 += (int)((group > 0 ? group : 0) * p.group_rows);
+            }
             for (int kb = 0; kb < num_k_blocks; kb++) {
                 if (round > 0 && !looked && !mbar_wait(empty0 + 8 * s, (round & 1) ^ 1, abort_flag, p.status, 101)) break;
                 const uint32_t bar = full0 + 8 * s, a_dst = tiles + s * STAGE_BYTES, b_dst = a_dst + A_TILE_BYTES;
@@ -1048,6 +1060,10 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
                     for (int q = 0; q < 8; q++)
                         o[q] = EPI == EPI_SWIGLU ? silu_mul(g[j8 + q] * row_scale, u[j8 + q] * row_scale)
                              : EPI == EPI_STORE ? g[j8 + q] * row_scale : g[j8 + q];
+                    if (EPI == EPI_STORE && p.act == 1) {
+#pragma unroll
+                        for (int q = 0; q < 8; q++) { const float z = fmaxf(o[q], 0.f); o[q] = z * z; }
+                    }
                     if (vec) {
                         if constexpr (sizeof(TC) == 4) {
                             float4* d4 = reinterpret_cast<float4*>(dst + j8);
@@ -1163,12 +1179,12 @@ struct Plan {
     int tiles;
 };
 
-bool make_plan(int T, int N, int K, int epilogue, int sm_count, Plan* plan) {
+bool make_plan(int T, int N, int K, int epilogue, int sm_count, Plan* plan, bool token_rows = false) {
     const int num_k_blocks = (K + BLOCK_K - 1) / BLOCK_K;
     Plan& pl = *plan;
     pl.sm_count = sm_count;
     pl.persistent = false;
-    pl.swapped = T <= 128;
+    pl.swapped = T <= 128 && !token_rows;   // (token_rows: the tokens stay on the 128-row side whatever their number)
     pl.splits = 1;
     int num_acc = 1;
     if (pl.swapped) {
@@ -1385,6 +1401,31 @@ HYMT2_API int hymt2_gemm_tc(void* C, int c_dtype, const void* X, const void* W, 
                             int num_counters, int* status, cudaStream_t stream) {
     return run_gemm_tc(C, c_dtype, X, W, T, N, K, lda, ldw, ldc, epilogue, workspace, workspace_floats, counters, num_counters,
                        status, stream, WAIT_LIMIT, -1);
+}
+
+// A grouped product on the persistent kernel: X holds tiles * 128 token rows sorted by group (segments of whole tiles),
+// W the groups' matrices [N, K] one after the other, tile_group[tile] the group of a row tile (-1: not in use).
+// C[tiles * 128, N] = act(X W[group]^T); act 0: as it is, 1: the square of relu.
+HYMT2_API int hymt2_gemm_tc_grouped(void* C, int c_dtype, const void* X, const void* W, const int* tile_group, int tiles, int groups,
+                                    int N, int K, long lda, long ldc, int act, int* status, cudaStream_t stream) {
+    if (tiles == 0 || N == 0) return HYMT2_OK;
+    HYMT2_REQUIRE(tiles > 0 && groups > 0 && N > 0 && K > 0 && tile_group, "gemm_tc_grouped: bad sizes tiles=%d groups=%d N=%d K=%d", tiles, groups, N, K);
+    HYMT2_REQUIRE(K % 8 == 0 && lda % 8 == 0 && N % 8 == 0, "gemm_tc_grouped: K, lda and N must be multiples of 8 (K=%d lda=%ld N=%d)", K, lda, N);
+    HYMT2_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_tc_grouped: operands must be 16-byte aligned");
+    HYMT2_REQUIRE(act == 0 || act == 1, "gemm_tc_grouped: unknown activation %d", act);
+    HYMT2_REQUIRE(status != nullptr, "gemm_tc_grouped: a status word is needed");
+    HYMT2_REQUIRE((long)tiles * TILE_M <= 2147483647L && (long)groups * N <= 2147483647L, "gemm_tc_grouped: too many rows");
+    const int T = tiles * TILE_M;
+    Plan pl;
+    make_plan(T, N, K, EPI_STORE, sm_count_of_current_device(), &pl, true);
+    CUtensorMap ma, mb;
+    const bool ok = make_map(&ma, X, T, K, lda, TILE_M) && make_map(&mb, W, (long)groups * N, K, K, pl.bn);
+    HYMT2_REQUIRE(ok, "gemm_tc_grouped: cuTensorMapEncodeTiled refused the operands");
+    GemmTcParams p{C, ldc, T, N, K, pl.stages, pl.bn, 1, pl.k_blocks_per_split, 0, nullptr, nullptr, status, RopeEpilogue{}, WAIT_LIMIT, -1, NormSide{}};
+    p.tile_group = tile_group;
+    p.group_rows = N;
+    p.act = act;
+    return launch_persistent(ma, mb, p, pl, EPI_STORE, c_dtype, stream);
 }
 
 // hymt2_gemm_tc with an RMSNorm folded in (see NormSide).  As a consumer (ss_in): the activations X are bf16(x * gain) and the sums

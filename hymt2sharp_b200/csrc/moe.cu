@@ -123,8 +123,10 @@ moe_place_kernel(int* __restrict__ pair_row, int* __restrict__ row_token, int* _
     const int padded = (mine + tile - 1) / tile * tile;
     for (int r = mine + threadIdx.x; r < padded; r += blockDim.x) row_token[base + r] = -1;
     for (int i = threadIdx.x; i < padded / tile; i += blockDim.x) tile_group[base / tile + i] = e;
-    if (e == (int)gridDim.x - 1)
+    if (e == (int)gridDim.x - 1) {   // behind the last segment: tiles that are not in use, rows that are nobody's
         for (int i = (base + padded) / tile + threadIdx.x; i < max_tiles; i += blockDim.x) tile_group[i] = -1;
+        for (long r = base + padded + threadIdx.x; r < (long)max_tiles * tile; r += blockDim.x) row_token[r] = -1;
+    }
 }
 
 // one block per token
@@ -146,7 +148,35 @@ moe_combine_kernel(float* __restrict__ out, const float* __restrict__ y, const T
     }
 }
 
+// xs[r] = x[row_token[r]] for the sorted rows (zeros for padding rows): the operand of a product whose tiles come by TMA
+template <typename T>
+__global__ void __launch_bounds__(128)
+moe_gather_kernel(T* __restrict__ xs, const T* __restrict__ x, const int* __restrict__ row_token, int width, bool vec) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t r = blockIdx.x;
+    const int t = row_token[r];
+    constexpr int V = 16 / sizeof(T);
+    if (vec) {
+        const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)(t < 0 ? 0 : t) * width);
+        uint4* dst = reinterpret_cast<uint4*>(xs + r * width);
+        for (int i = threadIdx.x; i < width / V; i += blockDim.x) dst[i] = t < 0 ? make_uint4(0, 0, 0, 0) : src[i];
+    } else {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) xs[r * width + i] = t < 0 ? from_float<T>(0.f) : x[(size_t)t * width + i];
+    }
+}
+
 }  // namespace
+
+HYMT2_API int hymt2_moe_gather(void* xs, const void* x, int dtype, const int* row_token, int rows, int width, cudaStream_t stream) {
+    if (rows == 0) return HYMT2_OK;
+    HYMT2_REQUIRE(rows > 0 && width > 0 && row_token, "moe_gather: bad sizes");
+    HYMT2_DISPATCH_DTYPE(dtype, T, {
+        const bool vec = width % (16 / sizeof(T)) == 0 && (uintptr_t)xs % 16 == 0 && (uintptr_t)x % 16 == 0;
+        launch_pdl(moe_gather_kernel<T>, dim3(rows), dim3(128), 0, stream, (T*)xs, (const T*)x, row_token, width, vec);
+    });
+    return hymt2_check_launch("moe_gather");
+}
 
 HYMT2_API int hymt2_moe_route(int* chosen, float* weight, const float* logits, const float* correction, int tokens, int outputs,
                               int top, cudaStream_t stream) {

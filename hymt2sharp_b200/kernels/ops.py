@@ -1217,15 +1217,7 @@ def rmsnorm_add_then_rows(residual: torch.Tensor, x: torch.Tensor, gain: torch.T
 
 # -- a mixture of experts ---------------------------------------------------------------------------------------------------------
 EPILOGUE_RELU_SQUARED = 3
-_group_tile = None
-
-
-def gemm_group_tile() -> int:
-    """Rows of a tile of the grouped product on CUDA cores: an expert's segment of sorted rows is padded to whole tiles."""
-    global _group_tile
-    if _group_tile is None:
-        _group_tile = int(_lib().hymt2_gemm_simt_group_tile())
-    return _group_tile
+_group_tiles: dict = {}
 
 
 def moe_route(chosen: torch.Tensor, weight: torch.Tensor, logits: torch.Tensor, correction: torch.Tensor | None) -> None:
@@ -1263,21 +1255,62 @@ def moe_place(pair_row: torch.Tensor, row_token: torch.Tensor, tile_group: torch
                                   c_int(experts), c_int(tile), c_int(tiles), _stream()), "moe_place", 2)
 
 
-def gemm_simt_grouped(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, tile_group: torch.Tensor, row_token: torch.Tensor,
-                      gather: bool, epilogue: int = EPILOGUE_STORE) -> None:
+GROUPED_KERNELS = ("simt", "skinny", "tc")
+
+
+def gemm_group_tile(kernel: str = "simt") -> int:
+    """Rows of a row tile of a grouped product (an expert's segment of sorted rows is padded to whole tiles): 64 for the
+    CUDA-core kernel, 8 for the one for few rows, 128 for the tensor-core kernel."""
+    if kernel not in _group_tiles:
+        _group_tiles[kernel] = 128 if kernel == "tc" else int(getattr(_lib(), f"hymt2_gemm_{kernel}_group_tile")())
+    return _group_tiles[kernel]
+
+
+def gemm_grouped(kernel: str, out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, tile_group: torch.Tensor, row_token: torch.Tensor,
+                 gather: bool, epilogue: int = EPILOGUE_STORE) -> None:
     """out[r] = epilogue(a[source(r)] @ w[tile_group[r // tile]]^T) for the sorted rows r of moe_place: w [experts, N, K];
     source(r) = row_token[r] with `gather` (a holds one row per token), r itself otherwise (a holds sorted rows); padding
-    rows and unused tiles are skipped.  Epilogues: EPILOGUE_STORE, EPILOGUE_RELU_SQUARED."""
+    rows and unused tiles are skipped ("tc": computed and never read).  Epilogues: EPILOGUE_STORE, EPILOGUE_RELU_SQUARED.
+    kernel "simt": CUDA cores, any sizes and types; "skinny": CUDA cores, tiles of 8 rows, a and w of one type, the time of
+    reading the weights once; "tc": tcgen05, bfloat16, no gather (see moe_gather), K and N multiples of 8."""
     _need(out, "out", None, 2); _need(a, "a", None, 2); _need(w, "w", None, 3)
     _need(tile_group, "tile_group", torch.int32, 1); _need(row_token, "row_token", torch.int32, 1)
-    tiles, tile = tile_group.numel(), gemm_group_tile()
+    tiles, tile = tile_group.numel(), gemm_group_tile(kernel)
     N, K = w.shape[1], w.shape[2]
     if out.shape != (tiles * tile, N) or a.shape[1] != K or row_token.numel() < tiles * tile or (not gather and a.shape[0] < tiles * tile):
-        raise KernelError(f"gemm_simt_grouped: shapes out {tuple(out.shape)} a {tuple(a.shape)} w {tuple(w.shape)} tiles {tiles}")
-    _check(_lib().hymt2_gemm_simt_grouped(_ptr(out), c_int(dtype_code(out.dtype)), _ptr(a), c_int(dtype_code(a.dtype)), _ptr(w),
-                                          c_int(dtype_code(w.dtype)), _ptr(tile_group), _ptr(row_token), c_int(1 if gather else 0),
-                                          c_int(tiles), c_int(N), c_int(K), c_long(a.stride(0)), c_long(out.stride(0)), c_long(N * K),
-                                          c_int(epilogue), _stream()), "gemm_simt_grouped")
+        raise KernelError(f"gemm_grouped: shapes out {tuple(out.shape)} a {tuple(a.shape)} w {tuple(w.shape)} tiles {tiles} of {tile}")
+    if kernel == "simt":
+        _check(_lib().hymt2_gemm_simt_grouped(_ptr(out), c_int(dtype_code(out.dtype)), _ptr(a), c_int(dtype_code(a.dtype)), _ptr(w),
+                                              c_int(dtype_code(w.dtype)), _ptr(tile_group), _ptr(row_token), c_int(1 if gather else 0),
+                                              c_int(tiles), c_int(N), c_int(K), c_long(a.stride(0)), c_long(out.stride(0)), c_long(N * K),
+                                              c_int(epilogue), _stream()), "gemm_simt_grouped")
+    elif kernel == "skinny":
+        if a.dtype != w.dtype:
+            raise KernelError("gemm_grouped: the kernel for few rows wants a and w of one type")
+        _check(_lib().hymt2_gemm_skinny_grouped(_ptr(out), c_int(dtype_code(out.dtype)), _ptr(a), _ptr(w), c_int(dtype_code(w.dtype)),
+                                                _ptr(tile_group), _ptr(row_token), c_int(1 if gather else 0), c_int(tiles), c_int(N), c_int(K),
+                                                c_long(a.stride(0)), c_long(out.stride(0)), c_long(N * K), c_int(epilogue), _stream()),
+               "gemm_skinny_grouped")
+    else:
+        if gather or a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+            raise KernelError("gemm_grouped: the tensor-core kernel wants sorted bfloat16 rows")
+        _check(_lib().hymt2_gemm_tc_grouped(_ptr(out), c_int(dtype_code(out.dtype)), _ptr(a), _ptr(w), _ptr(tile_group), c_int(tiles),
+                                            c_int(w.shape[0]), c_int(N), c_int(K), c_long(a.stride(0)), c_long(out.stride(0)),
+                                            c_int(1 if epilogue == EPILOGUE_RELU_SQUARED else 0), _ptr(device_status(out.device)), _stream()),
+               "gemm_tc_grouped")
+
+
+def gemm_simt_grouped(out, a, w, tile_group, row_token, gather: bool, epilogue: int = EPILOGUE_STORE) -> None:
+    gemm_grouped("simt", out, a, w, tile_group, row_token, gather, epilogue)
+
+
+def moe_gather(xs: torch.Tensor, x: torch.Tensor, row_token: torch.Tensor) -> None:
+    """xs[r] = x[row_token[r]] (zeros where row_token[r] < 0): the sorted rows side by side, for a product that cannot gather."""
+    _need(xs, "xs", x.dtype, 2); _need(x, "x", None, 2); _need(row_token, "row_token", torch.int32, 1)
+    if xs.shape[1] != x.shape[1] or row_token.numel() < xs.shape[0]:
+        raise KernelError(f"moe_gather: shapes xs {tuple(xs.shape)} x {tuple(x.shape)} rows {row_token.numel()}")
+    _check(_lib().hymt2_moe_gather(_ptr(xs), _ptr(x), c_int(dtype_code(x.dtype)), _ptr(row_token), c_int(xs.shape[0]), c_int(x.shape[1]),
+                                   _stream()), "moe_gather")
 
 
 def moe_combine(out: torch.Tensor, y: torch.Tensor, x: torch.Tensor, pair_row: torch.Tensor, weight: torch.Tensor, add: bool = False) -> None:

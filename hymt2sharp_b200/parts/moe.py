@@ -21,6 +21,7 @@ from .base import PartSpec, build_part, register_part
 from .linear import Linear, compute_form
 
 ACTIVATIONS = {"relu2": ops.EPILOGUE_RELU_SQUARED}
+SKINNY_MAX_PAIRS = 512   # up to this many (token, choice) pairs in a step the kernel for few rows runs the experts
 
 
 class RoutedExperts:
@@ -70,13 +71,25 @@ class RoutedExperts:
     def first_weights(self):
         return self.router.weight if self.router is not None else None
 
+    def _grouped_kernel(self, x: torch.Tensor, tokens: int) -> str:
+        """Which grouped product runs the experts: few (token, choice) pairs meet mostly different experts, and the step costs
+        what reading those experts' weights costs (the kernel for few rows); many pairs go to the tensor cores where the
+        operands are bfloat16 with rows in whole 16-byte pieces; everything else to the general CUDA-core kernel."""
+        same = self.up is not None and x.dtype == self.up.dtype
+        if same and tokens * self.top <= SKINNY_MAX_PAIRS:
+            return "skinny"
+        if same and x.dtype == torch.bfloat16 and self.hidden % 8 == 0 and self.intermediate % 8 == 0:
+            return "tc"
+        return "simt"
+
     def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx, store: bool = False) -> None:
         T, dev = x.shape[0], x.device
         logits = self.router(x, out_dtype=torch.float32, ctx=ctx)
         chosen = torch.empty((T, self.top), dtype=torch.int32, device=dev)
         weight = torch.empty((T, self.top), dtype=torch.float32, device=dev)
         ops.moe_route(chosen, weight, logits, self.correction)
-        tile = ops.gemm_group_tile()
+        kernel = self._grouped_kernel(x, T)
+        tile = ops.gemm_group_tile(kernel)
         tiles = ops.moe_tiles(T, self.top, self.experts, tile)
         ints = torch.empty(T * self.top + tiles * tile + tiles + max(self.experts, 1), dtype=torch.int32, device=dev)
         pair_row = ints[: T * self.top].view(T, self.top)
@@ -85,12 +98,16 @@ class RoutedExperts:
         counts = ints[T * self.top + tiles * tile + tiles:]
         ops.moe_place(pair_row, row_token, tile_group, counts, chosen, self.experts, tile)
         if self.experts:
+            rows, gather = x, True
+            if kernel == "tc":     # its tiles come by TMA, which reads rows side by side
+                rows, gather = torch.empty((tiles * tile, self.hidden), dtype=x.dtype, device=dev), False
+                ops.moe_gather(rows, x, row_token)
             act = torch.empty((tiles * tile, self.intermediate), dtype=x.dtype, device=dev)
             ops.tag = "experts_up"
-            ops.gemm_simt_grouped(act, x, self.up, tile_group, row_token, True, ACTIVATIONS[self.activation])
+            ops.gemm_grouped(kernel, act, rows, self.up, tile_group, row_token, gather, ACTIVATIONS[self.activation])
             y = torch.empty((tiles * tile, self.hidden), dtype=torch.float32, device=dev)
             ops.tag = "experts_down"
-            ops.gemm_simt_grouped(y, act, self.down, tile_group, row_token, False, ops.EPILOGUE_STORE)
+            ops.gemm_grouped(kernel, y, act, self.down, tile_group, row_token, False, ops.EPILOGUE_STORE)
             ops.tag = None
         else:
             y = torch.empty((1, self.hidden), dtype=torch.float32, device=dev)   # never read: every pair names an identity expert

@@ -264,12 +264,14 @@ def test_routing_against_the_plain_choice(outputs, top):
     assert torch.equal(chosen.cpu()[0].long(), torch.arange(top))
 
 
+@pytest.mark.parametrize("kernel", ["simt", "skinny", "tc"])
 @pytest.mark.parametrize("tokens, top, experts, identity", [(1, 1, 1, 0), (5, 2, 3, 2), (300, 3, 8, 4), (129, 4, 1, 3), (64, 2, 0, 3)])
-def test_sorted_rows_hold_every_pair_once_in_token_order(tokens, top, experts, identity):
+def test_sorted_rows_hold_every_pair_once_in_token_order(tokens, top, experts, identity, kernel):
     from hymt2sharp_b200.kernels import ops
     rng = np.random.default_rng(tokens)
     chosen = np.stack([rng.permutation(experts + identity)[:top] for _ in range(tokens)]).astype(np.int32)
-    tile = ops.gemm_group_tile()
+    tile = ops.gemm_group_tile(kernel)          # row tiles of 64, 8 and 128 rows
+    assert tile == {"simt": 64, "skinny": 8, "tc": 128}[kernel]
     tiles = ops.moe_tiles(tokens, top, experts, tile)
     c = torch.from_numpy(chosen).to(DEV)
     pair_row = torch.full((tokens, top), -7, dtype=torch.int32, device=DEV)
@@ -290,13 +292,17 @@ def test_sorted_rows_hold_every_pair_once_in_token_order(tokens, top, experts, i
                 if chosen[t, k] == e:
                     assert rt[pr[t, k]] == t and used <= pr[t, k] < used + len(ts)
         used += n
-    assert (tg[used // tile:] == -1).all()
+    assert (tg[used // tile:] == -1).all() and (rt[used:] == -1).all()
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("hidden, experts, identity, top, ff, shared, tokens", [
-    (42, 3, 2, 2, 11, 13, 70), (64, 8, 4, 3, 64, 128, 300), (40, 5, 0, 1, 8, None, 9), (48, 1, 3, 4, 5, 6, 1), (32, 0, 3, 2, 8, None, 20)])
+    (42, 3, 2, 2, 11, 13, 70), (64, 8, 4, 3, 64, 128, 300), (40, 5, 0, 1, 8, None, 9), (48, 1, 3, 4, 5, 6, 1), (32, 0, 3, 2, 8, None, 20),
+    (42, 3, 2, 2, 11, 13, 400), (128, 6, 1, 2, 72, None, 700)])
 def test_mixture_of_experts_against_plain(dtype, hidden, experts, identity, top, ff, shared, tokens):
+    """Few (token, choice) pairs run the grouped product for few rows; many run the tensor-core one in bfloat16 where rows are
+    whole 16-byte pieces (the cases of 300 and 700 tokens) and the general one otherwise (400 tokens of 42 entries, and every
+    32-bit case with many pairs)."""
     from hymt2sharp_b200.parts import PartSpec, build_part
     torch.manual_seed(hidden + tokens)
     sh = None if shared is None else PartSpec("dense_mlp", dict(hidden=hidden, intermediate=shared, activation="relu2",
@@ -307,6 +313,8 @@ def test_mixture_of_experts_against_plain(dtype, hidden, experts, identity, top,
     w = {n: (torch.randn(s.shape) * 0.3).to(torch.bfloat16) for n, s in part.tensors().items()}
     w["m.router"] = (w["m.router"].float() * 4).to(torch.bfloat16)
     part.load(w, DEV, dtype)
+    want = "skinny" if tokens * top <= 512 else ("tc" if dtype == torch.bfloat16 and hidden % 8 == 0 else "simt")
+    assert experts == 0 or part._grouped_kernel(torch.empty(1, dtype=dtype, device=DEV), tokens) == want
     x = torch.randn(tokens, hidden).to(torch.bfloat16).float()
     mlp = dict(router=dict(experts=experts, identity=identity, top=top), expert=dict(ff=ff), shared=None if shared is None else dict(ff=shared))
     ref = plain.mixture(x.to(F64), {k: v.to(F64) for k, v in w.items()}, "m.", mlp).numpy()
@@ -320,14 +328,14 @@ def test_mixture_of_experts_against_plain(dtype, hidden, experts, identity, top,
     res2 = torch.full((tokens, hidden), float("nan"), dtype=torch.float32, device=DEV)
     part.forward(xs, res2, ctx, store=True)                 # overwrites
     helpers.assert_close(res2.cpu().numpy(), ref, name, "mixture stored", factor=2.0)
-    # a token's row does not depend on the other tokens of the step (32-bit: to the bit; the tensor-core products of the
-    # bfloat16 engine turn their tiles round between few tokens and many, which shows in the last bits)
+    # a token's row does not depend on the other tokens of the step beyond rounding (few pairs and many run different
+    # grouped products, whose sums run in different orders)
     one = torch.zeros((1, hidden), dtype=torch.float32, device=DEV)
     part.forward(xs[tokens // 2: tokens // 2 + 1], one, ctx, store=True)
-    if dtype == torch.float32:
-        assert torch.equal(one[0], res2[tokens // 2])
-    else:
-        helpers.assert_close(one[0].cpu().numpy(), res2[tokens // 2].cpu().numpy(), name, "one token alone", factor=0.5)
+    helpers.assert_close(one[0].cpu().numpy(), res2[tokens // 2].cpu().numpy(), name, "one token alone", factor=0.5)
+    half = torch.zeros((tokens // 2 + 1, hidden), dtype=torch.float32, device=DEV)
+    part.forward(xs[: tokens // 2 + 1], half, ctx, store=True)
+    helpers.assert_close(half[-1].cpu().numpy(), res2[tokens // 2].cpu().numpy(), name, "half the tokens", factor=0.5)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
