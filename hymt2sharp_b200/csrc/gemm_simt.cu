@@ -294,19 +294,31 @@ gemm_skinny_grouped_kernel(TC* __restrict__ C, const T* __restrict__ A, const T*
     for (int m = 0; m < GROUP_SKINNY_ROWS; m++) acc[m] = 0.f;
     constexpr int V = 16 / sizeof(T);
     if (vec) {
-        for (int k = lane * V; k < K; k += 32 * V) {
-            float wv[V];
-            const uint4 raw = *reinterpret_cast<const uint4*>(w + k);
-            const T* wt = reinterpret_cast<const T*>(&raw);
+        // four pieces of the weight row in flight per lane: the kernel's time is the weights' way from memory
+        constexpr int U = 4;
+        for (int k0 = lane * V; k0 < K; k0 += 32 * V * U) {
+            uint4 raw[U];
 #pragma unroll
-            for (int i = 0; i < V; i++) wv[i] = to_float(wt[i]);
+            for (int u = 0; u < U; u++) {
+                const int k = k0 + u * 32 * V;
+                raw[u] = k < K ? __ldg(reinterpret_cast<const uint4*>(w + k)) : make_uint4(0, 0, 0, 0);
+            }
 #pragma unroll
-            for (int m = 0; m < GROUP_SKINNY_ROWS; m++) {
-                if (ok[m]) {
-                    const uint4 ra = *reinterpret_cast<const uint4*>(a_row[m] + k);
-                    const T* at = reinterpret_cast<const T*>(&ra);
+            for (int u = 0; u < U; u++) {
+                const int k = k0 + u * 32 * V;
+                if (k >= K) break;
+                float wv[V];
+                const T* wt = reinterpret_cast<const T*>(&raw[u]);
 #pragma unroll
-                    for (int i = 0; i < V; i++) acc[m] = fmaf(to_float(at[i]), wv[i], acc[m]);
+                for (int i = 0; i < V; i++) wv[i] = to_float(wt[i]);
+#pragma unroll
+                for (int m = 0; m < GROUP_SKINNY_ROWS; m++) {
+                    if (ok[m]) {
+                        const uint4 ra = *reinterpret_cast<const uint4*>(a_row[m] + k);
+                        const T* at = reinterpret_cast<const T*>(&ra);
+#pragma unroll
+                        for (int i = 0; i < V; i++) acc[m] = fmaf(to_float(at[i]), wv[i], acc[m]);
+                    }
                 }
             }
         }

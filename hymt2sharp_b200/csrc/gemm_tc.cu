@@ -126,8 +126,9 @@ struct GemmTcParams {
     NormSide norm;
     int together = 0;        // splits through the workspace: every CTA of a tile folds a share of its columns (all of them are resident)
     // A grouped product (persistent kernel only): the token rows are sorted by the weight matrix they meet, in segments of
-    // whole row tiles; tile_group[row tile] names the matrix (its rows start at group * group_rows of the weight map; a tile
-    // that is not in use says -1 and is computed against matrix 0, nobody reads its rows).  N is one matrix's rows.
+    // whole row tiles; tile_group[row tile] names the matrix (its rows start at group * group_rows of the weight map).  The
+    // tiles in use come first; tile_group[number of row tiles] says how many they are, and the others do not run.  N is one
+    // matrix's rows.
     const int* tile_group = nullptr;
     long group_rows = 0;
     int act = 0;             // store epilogue: 1 = the square of relu on the way out
@@ -900,7 +901,15 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     const uint32_t acc_full0 = smem_u32(&bars[2 * MAX_STAGES]), acc_empty0 = acc_full0 + 16;
     volatile int* abort_flag = &abort_s;
     const int num_k_blocks = (p.K + BLOCK_K - 1) / BLOCK_K;
-    const int tiles_m = (p.T + TILE_M - 1) / TILE_M, tiles_n = (p.N + OUT_COLS - 1) / OUT_COLS;
+    int tiles_m = (p.T + TILE_M - 1) / TILE_M;
+    const int tiles_n = (p.N + OUT_COLS - 1) / OUT_COLS;
+    if (p.tile_group) {
+        // a grouped product: the row tiles in use come first, and their number stands behind the last tile's entry (written by
+        // the kernel before, so every role waits for it here)
+        pdl_wait();
+        const int used = p.tile_group[tiles_m];
+        tiles_m = used < tiles_m ? (used > 0 ? used : 0) : tiles_m;
+    }
     const int num_tiles = tiles_m * tiles_n;
 
     if (threadIdx.x == 0) {
@@ -1404,7 +1413,8 @@ HYMT2_API int hymt2_gemm_tc(void* C, int c_dtype, const void* X, const void* W, 
 }
 
 // A grouped product on the persistent kernel: X holds tiles * 128 token rows sorted by group (segments of whole tiles),
-// W the groups' matrices [N, K] one after the other, tile_group[tile] the group of a row tile (-1: not in use).
+// W the groups' matrices [N, K] one after the other, tile_group[tile] the group of a row tile, tile_group[tiles] the number of
+// tiles in use (the first ones; the others do not run).
 // C[tiles * 128, N] = act(X W[group]^T); act 0: as it is, 1: the square of relu.
 HYMT2_API int hymt2_gemm_tc_grouped(void* C, int c_dtype, const void* X, const void* W, const int* tile_group, int tiles, int groups,
                                     int N, int K, long lda, long ldc, int act, int* status, cudaStream_t stream) {

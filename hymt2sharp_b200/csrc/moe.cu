@@ -9,7 +9,7 @@
 //            experts, which need no product)
 //   place    every expert's pairs, in token order, get consecutive rows of a sorted list; an expert's segment is padded to
 //            whole tiles of `tile` rows.  Written: pair_row[pair] (-1 for identity experts), row_token[row] (-1 for padding),
-//            tile_group[tile] (-1 for tiles not in use)
+//            tile_group[tile] (-1 for tiles not in use; the tiles in use come first, and their number follows the last entry)
 //   combine  out[t] = sum over the token's choices, in the order they were chosen, of weight * (the expert's output row, or
 //            the token's own input row for an identity expert)
 #include "common.cuh"
@@ -78,12 +78,15 @@ moe_count_kernel(int* __restrict__ counts, const int* __restrict__ chosen, int p
     if (threadIdx.x == 0) counts[e] = (int)total;
 }
 
+constexpr int PLACE_CHUNK = 8192;   // pairs that go through shared memory at a time
+
 __global__ void __launch_bounds__(PLACE_THREADS)
 moe_place_kernel(int* __restrict__ pair_row, int* __restrict__ row_token, int* __restrict__ tile_group,
                  const int* __restrict__ counts, const int* __restrict__ chosen, int pairs, int top, int experts, int tile,
                  int max_tiles) {
+    __shared__ int chunk[PLACE_CHUNK];
     __shared__ int warp_total[PLACE_THREADS / 32];
-    __shared__ int base_s, running_s;
+    __shared__ int base_s;
     pdl_wait();
     pdl_launch_dependents();
     const int e = blockIdx.x;
@@ -92,40 +95,56 @@ moe_place_kernel(int* __restrict__ pair_row, int* __restrict__ row_token, int* _
         int rows = 0;
         for (int i = 0; i < e; i++) rows += (counts[i] + tile - 1) / tile * tile;
         base_s = rows;
-        running_s = 0;
     }
     __syncthreads();
     const int base = base_s;
-    const int mine = counts[e];
-    for (int i0 = 0; i0 < pairs; i0 += PLACE_THREADS) {
-        const int i = i0 + threadIdx.x;
-        const int c = i < pairs ? chosen[i] : -1;
-        const bool hit = c == e && e < experts;
-        if (e == 0 && c >= experts) pair_row[i] = -1;
-        const unsigned ballot = __ballot_sync(0xffffffffu, hit);
-        if (lane == 0) warp_total[warp] = __popc(ballot);
+    int placed = 0;   // hits of the chunks so far
+    for (int c0 = 0; c0 < pairs; c0 += PLACE_CHUNK) {
+        const int n = min(PLACE_CHUNK, pairs - c0);
         __syncthreads();
-        int before = running_s;
-        for (int w = 0; w < warp; w++) before += warp_total[w];
-        if (hit) {
-            const int row = base + before + __popc(ballot & ((1u << lane) - 1u));
-            pair_row[i] = row;
-            row_token[row] = i / top;
+        for (int i = threadIdx.x; i < n; i += blockDim.x) chunk[i] = chosen[c0 + i];   // neighbours read neighbours
+        __syncthreads();
+        // A thread owns a run of consecutive pairs: it counts its hits, a scan over the threads' counts gives the place of
+        // its first hit, and a second walk over the run writes the rows.  Pairs keep their order.
+        const int run = (n + PLACE_THREADS - 1) / PLACE_THREADS;
+        const int i0 = min(n, (int)threadIdx.x * run), i1 = min(n, i0 + run);
+        int hits = 0;
+        if (e < experts)
+            for (int i = i0; i < i1; i++) hits += chunk[i] == e;
+        int incl = hits;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int up = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += up;
         }
+        if (lane == 31) warp_total[warp] = incl;
         __syncthreads();
-        if (threadIdx.x == 0) {
-            int all = 0;
-            for (int w = 0; w < PLACE_THREADS / 32; w++) all += warp_total[w];
-            running_s += all;
+        int before = incl - hits, all = 0;
+        for (int w = 0; w < PLACE_THREADS / 32; w++) {
+            if (w < warp) before += warp_total[w];
+            all += warp_total[w];
         }
-        __syncthreads();
+        int at = base + placed + before;
+        for (int i = i0; i < i1; i++) {
+            const int c = chunk[i];
+            if (c == e && e < experts) {
+                pair_row[c0 + i] = at;
+                row_token[at] = (c0 + i) / top;
+                at++;
+            } else if (e == 0 && c >= experts) {
+                pair_row[c0 + i] = -1;
+            }
+        }
+        placed += all;
     }
+    const int mine = counts[e];
     const int padded = (mine + tile - 1) / tile * tile;
     for (int r = mine + threadIdx.x; r < padded; r += blockDim.x) row_token[base + r] = -1;
     for (int i = threadIdx.x; i < padded / tile; i += blockDim.x) tile_group[base / tile + i] = e;
     if (e == (int)gridDim.x - 1) {   // behind the last segment: tiles that are not in use, rows that are nobody's
         for (int i = (base + padded) / tile + threadIdx.x; i < max_tiles; i += blockDim.x) tile_group[i] = -1;
         for (long r = base + padded + threadIdx.x; r < (long)max_tiles * tile; r += blockDim.x) row_token[r] = -1;
+        if (threadIdx.x == 0) tile_group[max_tiles] = (base + padded) / tile;   // how many tiles are in use: they come first
     }
 }
 
@@ -145,6 +164,115 @@ moe_combine_kernel(float* __restrict__ out, const float* __restrict__ y, const T
             acc = fmaf(weight[t * top + k], v, acc);
         }
         out[t * width + i] = acc;
+    }
+}
+
+// A step of few tokens in one block: the routing of every token, then the sorted rows, with what the three kernels above
+// leave behind (chosen, weight, pair_row, row_token, tile_group).  A thread owns an expert and walks the pairs in order.
+constexpr int SMALL_PAIRS = 1024, SMALL_THREADS = 256;
+
+__global__ void __launch_bounds__(SMALL_THREADS)
+moe_route_place_small_kernel(int* __restrict__ chosen, float* __restrict__ weight, int* __restrict__ pair_row, int* __restrict__ row_token,
+                             int* __restrict__ tile_group, const float* __restrict__ logits, const float* __restrict__ correction,
+                             int tokens, int outputs, int top, int experts, int tile, int max_tiles) {
+    extern __shared__ float smem[];   // [warps][2 * outputs] scores and choice scores, then [experts + 1] segment starts
+    __shared__ int pairs_s[SMALL_PAIRS];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = SMALL_THREADS / 32;
+    float* s = smem + (size_t)warp * 2 * outputs;
+    float* c = s + outputs;
+    int* start = reinterpret_cast<int*>(smem + (size_t)warps * 2 * outputs);
+    for (int t = warp; t < tokens; t += warps) {
+        const float* z = logits + (size_t)t * outputs;
+        float m = -INFINITY;
+        for (int i = lane; i < outputs; i += 32) m = fmaxf(m, z[i]);
+        m = warp_max(m);
+        float sum = 0.f;
+        for (int i = lane; i < outputs; i += 32) { const float e = expf(z[i] - m); s[i] = e; sum += e; }
+        sum = warp_sum(sum);
+        const float inv = 1.0f / sum;
+        for (int i = lane; i < outputs; i += 32) {
+            s[i] *= inv;
+            c[i] = s[i] + (correction ? correction[i] : 0.f);
+        }
+        __syncwarp();
+        for (int k = 0; k < top; k++) {
+            float best = -INFINITY;
+            int at = 0x7fffffff;
+            for (int i = lane; i < outputs; i += 32)
+                if (c[i] > best) { best = c[i]; at = i; }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+                if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+            }
+            if (lane == 0) {
+                chosen[(size_t)t * top + k] = at;
+                weight[(size_t)t * top + k] = s[at];
+                pairs_s[t * top + k] = at;
+                c[at] = -INFINITY;
+            }
+            __syncwarp();
+        }
+    }
+    __syncthreads();
+    const int pairs = tokens * top;
+    for (int e = threadIdx.x; e < experts; e += SMALL_THREADS) {
+        int n = 0;
+        for (int i = 0; i < pairs; i++) n += pairs_s[i] == e;
+        start[e + 1] = (n + tile - 1) / tile * tile;   // the segment's padded length for now
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        start[0] = 0;
+        for (int e = 0; e < experts; e++) start[e + 1] += start[e];
+        tile_group[max_tiles] = start[experts] / tile;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < experts; e += SMALL_THREADS) {
+        int at = start[e];
+        for (int i = 0; i < pairs; i++)
+            if (pairs_s[i] == e) { pair_row[i] = at; row_token[at] = i / top; at++; }
+        for (; at < start[e + 1]; at++) row_token[at] = -1;
+        for (int i = start[e] / tile; i < start[e + 1] / tile; i++) tile_group[i] = e;
+    }
+    for (int i = threadIdx.x; i < pairs; i += SMALL_THREADS)
+        if (pairs_s[i] >= experts) pair_row[i] = -1;
+    const int used = start[experts];
+    for (int i = used / tile + threadIdx.x; i < max_tiles; i += SMALL_THREADS) tile_group[i] = -1;
+    for (int r = used + threadIdx.x; r < max_tiles * tile; r += SMALL_THREADS) row_token[r] = -1;
+}
+
+// The mixture's last step and the norm behind the sublayer in one pass over a token's row:
+//   v = (branch[t] if given) + sum_k weight[t, k] * (y[pair_row[t, k]] or x[t]);  residual[t] += v / rms(v) * gain;  rows[t] = residual[t] rounded
+template <typename TX, typename TW, typename TH>
+__global__ void __launch_bounds__(256)
+moe_combine_norm_kernel(float* __restrict__ residual, TH* __restrict__ rows, const float* __restrict__ branch, const float* __restrict__ y,
+                        const TX* __restrict__ x, const int* __restrict__ pair_row, const float* __restrict__ weight,
+                        const TW* __restrict__ gain, int width, int top, float eps) {
+    extern __shared__ float smem[];   // [width] the row, then 33 floats for the block sum
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t t = blockIdx.x;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float acc = branch ? branch[t * width + i] : 0.f;
+        for (int k = 0; k < top; k++) {
+            const int row = pair_row[t * top + k];
+            const float v = row >= 0 ? y[(size_t)row * width + i] : to_float(x[t * width + i]);
+            acc = fmaf(weight[t * top + k], v, acc);
+        }
+        smem[i] = acc;
+        ss = fmaf(acc, acc, ss);
+    }
+    ss = block_sum(ss, smem + width);
+    const float scale = 1.0f / sqrtf(ss / (float)width + eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = residual[t * width + i] + smem[i] * scale * to_float(gain[i]);
+        residual[t * width + i] = v;
+        if (rows) rows[t * width + i] = from_float<TH>(v);
     }
 }
 
@@ -190,7 +318,7 @@ HYMT2_API int hymt2_moe_route(int* chosen, float* weight, const float* logits, c
 }
 
 // counts [experts] is scratch; row_token holds pairs + experts * (tile - 1) rows rounded up to whole tiles, tile_group one entry
-// for each of those tiles (max_tiles).
+// for each of those tiles (max_tiles) and one more, which receives the number of tiles in use (they are the first ones).
 HYMT2_API int hymt2_moe_place(int* pair_row, int* row_token, int* tile_group, int* counts, const int* chosen, int tokens, int top,
                               int experts, int tile, int max_tiles, cudaStream_t stream) {
     if (tokens == 0) return HYMT2_OK;
@@ -212,4 +340,33 @@ HYMT2_API int hymt2_moe_combine(float* out, const float* y, const void* x, int x
     HYMT2_DISPATCH_DTYPE(x_dtype, TX, (launch_pdl(moe_combine_kernel<TX>, dim3(tokens), dim3(256), 0, stream, out, y, (const TX*)x, pair_row,
                                                   weight, width, top, add)));
     return hymt2_check_launch("moe_combine");
+}
+
+// moe_route and moe_place in one launch for a step of few tokens (tokens * top <= 1024, experts <= 4096).
+HYMT2_API int hymt2_moe_route_place_small(int* chosen, float* weight, int* pair_row, int* row_token, int* tile_group, const float* logits,
+                                          const float* correction, int tokens, int outputs, int top, int experts, int tile, int max_tiles,
+                                          cudaStream_t stream) {
+    if (tokens == 0) return HYMT2_OK;
+    HYMT2_REQUIRE(tokens > 0 && outputs > 0 && top > 0 && top <= outputs && experts >= 0 && experts <= outputs && tile > 0, "moe_route_place_small: bad sizes");
+    HYMT2_REQUIRE((long)tokens * top <= SMALL_PAIRS, "moe_route_place_small: %d pairs are too many", tokens * top);
+    HYMT2_REQUIRE(experts == 0 || (long)max_tiles * tile >= (long)tokens * top + (long)experts * (tile - 1), "moe_route_place_small: too few tiles");
+    const size_t smem = ((size_t)(SMALL_THREADS / 32) * 2 * outputs + experts + 1) * sizeof(float);
+    HYMT2_REQUIRE(smem <= 40 * 1024, "moe_route_place_small: %d router outputs are too many", outputs);
+    launch_pdl(moe_route_place_small_kernel, dim3(1), dim3(SMALL_THREADS), smem, stream, chosen, weight, pair_row, row_token, tile_group,
+               logits, correction, tokens, outputs, top, experts, tile, max_tiles);
+    return hymt2_check_launch("moe_route_place");
+}
+
+// residual += norm(branch + the chosen experts' rows) with the norm's gain; rows (may be null) = the new residual rows in their type.
+HYMT2_API int hymt2_moe_combine_norm(float* residual, void* rows, int rows_dtype, const float* branch, const float* y, const void* x,
+                                     int x_dtype, const int* pair_row, const float* weight, const void* gain, int gain_dtype, int tokens,
+                                     int width, int top, float eps, cudaStream_t stream) {
+    if (tokens == 0) return HYMT2_OK;
+    HYMT2_REQUIRE(tokens > 0 && width > 0 && top > 0, "moe_combine_norm: bad sizes");
+    const size_t smem = ((size_t)width + 33) * sizeof(float);
+    HYMT2_REQUIRE(smem <= 48 * 1024, "moe_combine_norm: rows of %d entries are too wide", width);
+    HYMT2_DISPATCH_DTYPE(x_dtype, TX, HYMT2_DISPATCH_DTYPE(gain_dtype, TW, HYMT2_DISPATCH_DTYPE(rows_dtype, TH,
+        (launch_pdl(moe_combine_norm_kernel<TX, TW, TH>, dim3(tokens), dim3(256), smem, stream, residual, (TH*)rows, branch, y, (const TX*)x,
+                    pair_row, weight, (const TW*)gain, width, top, eps)))));
+    return hymt2_check_launch("moe_combine_norm");
 }

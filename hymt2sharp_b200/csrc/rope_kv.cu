@@ -126,6 +126,70 @@ rope_kv_kernel(RopeKvParams p, int tokens) {
     }
 }
 
+// The norm over a token's whole projection (NORM_ALL_BEFORE) with a block per token: the q and k sections go to shared
+// memory once, the two sums of squares are block sums, then every warp norms, rotates and writes heads.  (With a warp per
+// head, as above, every head's warp reads the whole section again for its sum.)
+template <typename T, typename TG>
+__global__ void __launch_bounds__(256)
+rope_kv_token_kernel(RopeKvParams p) {
+    extern __shared__ float smem[];   // [nh * d | nkv * d] the token's queries and keys, then 33 floats for the block sums
+    pdl_wait();
+    pdl_launch_dependents();
+    const int t = blockIdx.x, d = p.d, dv = p.dv, half = p.rope_dim / 2;
+    const int q_cols = p.nh * d, k_cols = p.has_kv ? p.nkv * d : 0;
+    float* scratch = smem + q_cols + k_cols;
+    const size_t in_row = (size_t)q_cols + (p.has_kv ? (size_t)p.nkv * (d + dv) : 0);
+    const T* tok = (const T*)p.qkv + (size_t)t * in_row;
+    const int pos = p.token_pos[t];
+    const int slot = p.slot_ids[p.token_seq[t]];
+    const bool write_kv = p.write_kv && slot >= 0;
+    float ssq = 0.f, ssk = 0.f;
+    for (int c = threadIdx.x; c < q_cols; c += blockDim.x) { const float v = to_float(tok[c]); smem[c] = v; ssq = fmaf(v, v, ssq); }
+    for (int c = threadIdx.x; c < k_cols; c += blockDim.x) { const float v = to_float(tok[q_cols + c]); smem[q_cols + c] = v; ssk = fmaf(v, v, ssk); }
+    ssq = block_sum(ssq, scratch);
+    const float scale_q = 1.0f / sqrtf(ssq / (float)q_cols + p.eps);
+    float scale_k = 0.f;
+    if (k_cols) {
+        ssk = block_sum(ssk, scratch);
+        scale_k = 1.0f / sqrtf(ssk / (float)k_cols + p.eps);
+    }
+    __syncthreads();
+    size_t cache_row0 = 0;
+    if (write_kv) {
+        const int block = p.block_table[(size_t)slot * p.table_stride + pos / p.block_tokens];
+        cache_row0 = (size_t)block * p.nkv * p.block_tokens + (pos % p.block_tokens);
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    const int heads = p.nh + (write_kv ? p.nkv : 0);
+    for (int head = warp; head < heads; head += warps) {
+        const bool is_q = head < p.nh;
+        const int kvh = head - p.nh;
+        float* row = smem + (size_t)head * d;     // (the k section follows the q section, head after head)
+        const TG* gain = (const TG*)(is_q ? p.q_gain : p.k_gain) + (size_t)(is_q ? head : kvh) * d;
+        const float scale = is_q ? scale_q : scale_k;
+        for (int c = lane; c < d; c += 32) row[c] = row[c] * scale * to_float(gain[c]);
+        __syncwarp();
+        for (int i = lane; i < half; i += 32) {
+            float sn, cs;
+            sincosf((float)pos * p.inv_freq[i], &sn, &cs);
+            const float x0 = row[i], x1 = row[i + half];
+            row[i] = x0 * cs - x1 * sn;
+            row[i + half] = x0 * sn + x1 * cs;
+        }
+        __syncwarp();
+        T* dst = is_q ? (T*)p.q_out + ((size_t)t * p.nh + head) * d
+                      : (T*)p.k_cache + (cache_row0 + (size_t)kvh * p.block_tokens) * d;
+        for (int c = lane; c < d; c += 32) dst[c] = from_float<T>(row[c]);
+    }
+    if (write_kv) {
+        const T* v = tok + q_cols + k_cols;
+        for (int c = threadIdx.x; c < p.nkv * dv; c += blockDim.x) {
+            const int kvh = c / dv, x = c - kvh * dv;
+            ((T*)p.v_cache)[(cache_row0 + (size_t)kvh * p.block_tokens) * dv + x] = v[c];
+        }
+    }
+}
+
 // bfloat16 with the whole head rotated (rope_dim == d, d = 64, 128 or 256): one warp per (token, head),
 // every lane holds E = d / 32 neighbouring values (one 4-, 8- or 16-byte load), the partner of a value
 // sits 16 lanes away, the sum of squares is a warp sum, nothing goes through shared memory.
@@ -243,6 +307,12 @@ HYMT2_API int hymt2_rope_kv_general(const void* qkv, void* q_out, void* k_cache,
     const long items = (long)tokens * (nh + (has_kv ? 2 * nkv : 0));
     HYMT2_REQUIRE((items + 3) / 4 <= 2147483647L, "rope_kv: too many (token, head) pairs");
     const unsigned blocks = (unsigned)((items + 3) / 4);
+    const size_t token_smem = ((size_t)(nh + (has_kv ? nkv : 0)) * d + 33) * sizeof(float);
+    if (norm_mode == NORM_ALL_BEFORE && token_smem <= 48 * 1024) {
+        HYMT2_DISPATCH_DTYPE(dtype, T, HYMT2_DISPATCH_DTYPE(gain_dtype, TG,
+            (launch_pdl(rope_kv_token_kernel<T, TG>, dim3(tokens), dim3(256), token_smem, stream, p))));
+        return hymt2_check_launch("rope_kv");
+    }
     HYMT2_DISPATCH_DTYPE(dtype, T, HYMT2_DISPATCH_DTYPE(gain_dtype, TG,
         (launch_pdl(rope_kv_kernel<T, TG>, dim3(blocks), dim3(128), smem, stream, p, tokens))));
     return hymt2_check_launch("rope_kv");

@@ -1242,12 +1242,12 @@ def moe_place(pair_row: torch.Tensor, row_token: torch.Tensor, tile_group: torch
               experts: int, tile: int) -> None:
     """Sorts the (token, choice) pairs of chosen [T, top] by expert, tokens in order inside an expert, each expert's rows padded
     to whole tiles: pair_row [T, top] = a pair's row in the sorted list (-1: it names an identity expert, index >= experts),
-    row_token [tiles * tile] = the token of a sorted row (-1: padding), tile_group [tiles] = the expert of a row tile (-1: not
-    in use).  counts [max(experts, 1)] is scratch."""
+    row_token [tiles * tile] = the token of a sorted row (-1: padding), tile_group [tiles + 1] = the expert of a row tile (-1: not
+    in use; the tiles in use come first) and, in its last entry, the number of tiles in use.  counts [max(experts, 1)] is scratch."""
     for t, n in ((pair_row, "pair_row"), (row_token, "row_token"), (tile_group, "tile_group"), (counts, "counts"), (chosen, "chosen")):
         _need(t, n, torch.int32)
     T, top = chosen.shape
-    tiles = tile_group.numel()
+    tiles = tile_group.numel() - 1
     if pair_row.shape != chosen.shape or row_token.numel() < tiles * tile or tiles < moe_tiles(T, top, experts, tile) \
             or counts.numel() < max(experts, 1):
         raise KernelError("moe_place: a buffer is too small")
@@ -1275,7 +1275,7 @@ def gemm_grouped(kernel: str, out: torch.Tensor, a: torch.Tensor, w: torch.Tenso
     reading the weights once; "tc": tcgen05, bfloat16, no gather (see moe_gather), K and N multiples of 8."""
     _need(out, "out", None, 2); _need(a, "a", None, 2); _need(w, "w", None, 3)
     _need(tile_group, "tile_group", torch.int32, 1); _need(row_token, "row_token", torch.int32, 1)
-    tiles, tile = tile_group.numel(), gemm_group_tile(kernel)
+    tiles, tile = tile_group.numel() - 1, gemm_group_tile(kernel)
     N, K = w.shape[1], w.shape[2]
     if out.shape != (tiles * tile, N) or a.shape[1] != K or row_token.numel() < tiles * tile or (not gather and a.shape[0] < tiles * tile):
         raise KernelError(f"gemm_grouped: shapes out {tuple(out.shape)} a {tuple(a.shape)} w {tuple(w.shape)} tiles {tiles} of {tile}")
@@ -1368,3 +1368,50 @@ def attention_decode_kv(out: torch.Tensor, q: torch.Tensor, k_plane: torch.Tenso
                                             _ptr(kv_lens), c_int(rows), c_int(nh), c_int(nkv), c_int(d), c_int(dv), c_float(scale),
                                             c_int(window), c_int(1 if sink else 0), c_int(max_splits), _ptr(part_acc), _ptr(part_ml),
                                             _ptr(counters), _stream()), "attention_decode")
+
+
+MOE_SMALL_PAIRS = 256   # up to this many (token, choice) pairs one block routes and sorts a step
+
+
+def moe_route_place(chosen: torch.Tensor, weight: torch.Tensor, pair_row: torch.Tensor, row_token: torch.Tensor, tile_group: torch.Tensor,
+                    logits: torch.Tensor, correction: torch.Tensor | None, experts: int, tile: int) -> None:
+    """moe_route and moe_place in one launch, for a step of at most MOE_SMALL_PAIRS (token, choice) pairs."""
+    _need(logits, "logits", torch.float32, 2); _need(chosen, "chosen", torch.int32, 2); _need(weight, "weight", torch.float32, 2)
+    for t, n in ((pair_row, "pair_row"), (row_token, "row_token"), (tile_group, "tile_group")):
+        _need(t, n, torch.int32)
+    T, R = logits.shape
+    top, tiles = chosen.shape[1], tile_group.numel() - 1
+    if chosen.shape[0] != T or weight.shape != chosen.shape or pair_row.shape != chosen.shape or not (0 < top <= R) or T * top > MOE_SMALL_PAIRS \
+            or row_token.numel() < tiles * tile or tiles < moe_tiles(T, top, experts, tile):
+        raise KernelError("moe_route_place: shapes do not fit, or a buffer is too small")
+    _f32(correction, "correction", R)
+    _check(_lib().hymt2_moe_route_place_small(_ptr(chosen), _ptr(weight), _ptr(pair_row), _ptr(row_token), _ptr(tile_group), _ptr(logits),
+                                              _ptr(correction), c_int(T), c_int(R), c_int(top), c_int(experts), c_int(tile), c_int(tiles),
+                                              _stream()), "moe_route_place")
+
+
+MOE_COMBINE_NORM_MAX_WIDTH = 12000   # a row of the fused combine-and-norm kernel lies in shared memory
+
+
+def moe_combine_norm(residual: torch.Tensor, rows: torch.Tensor | None, branch: torch.Tensor | None, y: torch.Tensor, x: torch.Tensor,
+                     pair_row: torch.Tensor, weight: torch.Tensor, gain: torch.Tensor, eps: float) -> None:
+    """v[t] = (branch[t] if given) + sum_k weight[t, k] * (y[pair_row[t, k]] if pair_row[t, k] >= 0 else x[t]); residual[t] (float32)
+    += v[t] / sqrt(mean(v[t]^2) + eps) * gain; rows[t] (if given) = the new residual row in rows' type."""
+    _need(residual, "residual", torch.float32, 2); _need(y, "y", torch.float32, 2); _need(x, "x", None, 2)
+    _need(pair_row, "pair_row", torch.int32, 2); _need(weight, "weight", torch.float32, 2); _need(gain, "gain", None, 1)
+    T, H = residual.shape
+    if x.shape != residual.shape or y.shape[1] != H or pair_row.shape[0] != T or weight.shape != pair_row.shape or gain.shape[0] != H \
+            or H > MOE_COMBINE_NORM_MAX_WIDTH:
+        raise KernelError(f"moe_combine_norm: shapes residual {tuple(residual.shape)} y {tuple(y.shape)} x {tuple(x.shape)}")
+    if branch is not None:
+        _need(branch, "branch", torch.float32, 2)
+        if branch.shape != residual.shape:
+            raise KernelError("moe_combine_norm: branch and residual differ in shape")
+    if rows is not None:
+        _need(rows, "rows", None, 2)
+        if rows.shape != residual.shape:
+            raise KernelError("moe_combine_norm: rows and residual differ in shape")
+    _check(_lib().hymt2_moe_combine_norm(_ptr(residual), _ptr(rows), c_int(dtype_code(rows.dtype) if rows is not None else F32), _ptr(branch),
+                                         _ptr(y), _ptr(x), c_int(dtype_code(x.dtype)), _ptr(pair_row), _ptr(weight), _ptr(gain),
+                                         c_int(dtype_code(gain.dtype)), c_int(T), c_int(H), c_int(pair_row.shape[1]), c_float(eps), _stream()),
+           "moe_combine_norm")

@@ -153,6 +153,14 @@ class SandwichBlock:
             h = self.norm1_after.add_into_then_rows(branch, residual, ctx.dtype)
         if self.conv2 is not None:
             h = self.conv2.forward(h, ctx, conv_slots.pop(0))
+        if hasattr(self.feed_forward, "forward_then_norm"):
+            # a feed-forward that adds its own pieces up can norm them and add them to the residual on the way
+            want = ctx.dtype if self.norm1 is None and ctx.dtype != residual.dtype else None
+            rows = self.feed_forward.forward_then_norm(h, residual, self.norm2_after, ctx, want)
+            if rows is not False:
+                if rows is not None:
+                    ctx.shared["residual_rows"] = (residual, rows)
+                return
         if getattr(self.feed_forward, "can_store", False):
             self.feed_forward.forward(h, branch, ctx, store=True)
         else:

@@ -82,39 +82,66 @@ class RoutedExperts:
             return "tc"
         return "simt"
 
-    def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx, store: bool = False) -> None:
+    def _experts(self, x: torch.Tensor, ctx):
+        """Routing, the sorted rows and the experts' products: (y, pair_row, weight), y float32 [sorted rows, hidden]."""
         T, dev = x.shape[0], x.device
         logits = self.router(x, out_dtype=torch.float32, ctx=ctx)
         chosen = torch.empty((T, self.top), dtype=torch.int32, device=dev)
         weight = torch.empty((T, self.top), dtype=torch.float32, device=dev)
-        ops.moe_route(chosen, weight, logits, self.correction)
         kernel = self._grouped_kernel(x, T)
         tile = ops.gemm_group_tile(kernel)
         tiles = ops.moe_tiles(T, self.top, self.experts, tile)
-        ints = torch.empty(T * self.top + tiles * tile + tiles + max(self.experts, 1), dtype=torch.int32, device=dev)
+        ints = torch.empty(T * self.top + tiles * tile + tiles + 1 + max(self.experts, 1), dtype=torch.int32, device=dev)
         pair_row = ints[: T * self.top].view(T, self.top)
         row_token = ints[T * self.top: T * self.top + tiles * tile]
-        tile_group = ints[T * self.top + tiles * tile: T * self.top + tiles * tile + tiles]
-        counts = ints[T * self.top + tiles * tile + tiles:]
-        ops.moe_place(pair_row, row_token, tile_group, counts, chosen, self.experts, tile)
-        if self.experts:
-            rows, gather = x, True
-            if kernel == "tc":     # its tiles come by TMA, which reads rows side by side
-                rows, gather = torch.empty((tiles * tile, self.hidden), dtype=x.dtype, device=dev), False
-                ops.moe_gather(rows, x, row_token)
-            act = torch.empty((tiles * tile, self.intermediate), dtype=x.dtype, device=dev)
-            ops.tag = "experts_up"
-            ops.gemm_grouped(kernel, act, rows, self.up, tile_group, row_token, gather, ACTIVATIONS[self.activation])
-            y = torch.empty((tiles * tile, self.hidden), dtype=torch.float32, device=dev)
-            ops.tag = "experts_down"
-            ops.gemm_grouped(kernel, y, act, self.down, tile_group, row_token, False, ops.EPILOGUE_STORE)
-            ops.tag = None
+        tile_group = ints[T * self.top + tiles * tile: T * self.top + tiles * tile + tiles + 1]   # and the number of tiles in use
+        counts = ints[T * self.top + tiles * tile + tiles + 1:]
+        if T * self.top <= ops.MOE_SMALL_PAIRS and self.outputs <= 512:
+            ops.moe_route_place(chosen, weight, pair_row, row_token, tile_group, logits, self.correction, self.experts, tile)
         else:
-            y = torch.empty((1, self.hidden), dtype=torch.float32, device=dev)   # never read: every pair names an identity expert
+            ops.moe_route(chosen, weight, logits, self.correction)
+            ops.moe_place(pair_row, row_token, tile_group, counts, chosen, self.experts, tile)
+        if not self.experts:
+            return torch.empty((1, self.hidden), dtype=torch.float32, device=dev), pair_row, weight   # y is never read
+        rows, gather = x, True
+        if kernel == "tc":     # its tiles come by TMA, which reads rows side by side
+            rows, gather = torch.empty((tiles * tile, self.hidden), dtype=x.dtype, device=dev), False
+            ops.moe_gather(rows, x, row_token)
+        act = torch.empty((tiles * tile, self.intermediate), dtype=x.dtype, device=dev)
+        ops.tag = "experts_up"
+        ops.gemm_grouped(kernel, act, rows, self.up, tile_group, row_token, gather, ACTIVATIONS[self.activation])
+        y = torch.empty((tiles * tile, self.hidden), dtype=torch.float32, device=dev)
+        ops.tag = "experts_down"
+        ops.gemm_grouped(kernel, y, act, self.down, tile_group, row_token, False, ops.EPILOGUE_STORE)
+        ops.tag = None
+        return y, pair_row, weight
+
+    def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx, store: bool = False) -> None:
+        y, pair_row, weight = self._experts(x, ctx)
         ops.moe_combine(residual, y, x, pair_row, weight, add=not store)
         if self.shared is not None:
             self.shared.forward(x, residual, ctx)
         ctx.prenormed = None
+
+    def forward_then_norm(self, x: torch.Tensor, residual: torch.Tensor, norm, ctx, rows_dtype=None):
+        """residual += norm(mixture(x)) for a block whose norm stands behind the sublayer: the experts' rows are added up,
+        normed and added to the residual by one kernel.  Returns the new residual rows rounded to `rows_dtype` (None: not
+        wanted), or False when this part cannot do it for this norm (the block then goes the long way)."""
+        if getattr(norm, "groups", 1) != 1 or self.hidden > ops.MOE_COMBINE_NORM_MAX_WIDTH or norm.dim != self.hidden:
+            return False
+        branch = None
+        if self.shared is not None:
+            branch = torch.empty_like(residual)
+            if getattr(self.shared, "can_store", False):
+                self.shared.forward(x, branch, ctx, store=True)
+            else:
+                branch.zero_()
+                self.shared.forward(x, branch, ctx)
+        y, pair_row, weight = self._experts(x, ctx)
+        rows = torch.empty(residual.shape, dtype=rows_dtype, device=residual.device) if rows_dtype is not None else None
+        ops.moe_combine_norm(residual, rows, branch, y, x, pair_row, weight, norm.gain, norm.eps)
+        ctx.prenormed = None
+        return rows
 
 
 register_part("feed_forward", "routed_experts", RoutedExperts)

@@ -265,7 +265,7 @@ def test_routing_against_the_plain_choice(outputs, top):
 
 
 @pytest.mark.parametrize("kernel", ["simt", "skinny", "tc"])
-@pytest.mark.parametrize("tokens, top, experts, identity", [(1, 1, 1, 0), (5, 2, 3, 2), (300, 3, 8, 4), (129, 4, 1, 3), (64, 2, 0, 3)])
+@pytest.mark.parametrize("tokens, top, experts, identity", [(1, 1, 1, 0), (5, 2, 3, 2), (300, 3, 8, 4), (129, 4, 1, 3), (64, 2, 0, 3), (3000, 3, 8, 4)])
 def test_sorted_rows_hold_every_pair_once_in_token_order(tokens, top, experts, identity, kernel):
     from hymt2sharp_b200.kernels import ops
     rng = np.random.default_rng(tokens)
@@ -276,7 +276,7 @@ def test_sorted_rows_hold_every_pair_once_in_token_order(tokens, top, experts, i
     c = torch.from_numpy(chosen).to(DEV)
     pair_row = torch.full((tokens, top), -7, dtype=torch.int32, device=DEV)
     row_token = torch.full((tiles * tile,), -7, dtype=torch.int32, device=DEV)
-    tile_group = torch.full((tiles,), -7, dtype=torch.int32, device=DEV)
+    tile_group = torch.full((tiles + 1,), -7, dtype=torch.int32, device=DEV)
     counts = torch.zeros(max(experts, 1), dtype=torch.int32, device=DEV)
     ops.moe_place(pair_row, row_token, tile_group, counts, c, experts, tile)
     pr, rt, tg = pair_row.cpu().numpy(), row_token.cpu().numpy(), tile_group.cpu().numpy()
@@ -292,7 +292,7 @@ def test_sorted_rows_hold_every_pair_once_in_token_order(tokens, top, experts, i
                 if chosen[t, k] == e:
                     assert rt[pr[t, k]] == t and used <= pr[t, k] < used + len(ts)
         used += n
-    assert (tg[used // tile:] == -1).all() and (rt[used:] == -1).all()
+    assert (tg[used // tile:tiles] == -1).all() and (rt[used:] == -1).all() and tg[tiles] == used // tile
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -394,3 +394,64 @@ def test_block_with_norms_behind_the_sublayers_only(dtype):
             left = ctx.shared.get("residual_rows")
             assert left is not None and left[0] is res and torch.equal(left[1], res.to(torch.bfloat16))
     helpers.assert_close(res.cpu().numpy(), r.numpy(), "float32" if dtype == torch.float32 else "bfloat16", "two blocks", factor=2.0)
+
+
+@pytest.mark.parametrize("tokens, top, experts, identity", [(1, 1, 1, 0), (5, 2, 3, 2), (64, 4, 32, 2), (20, 3, 0, 4), (9, 4, 1, 3)])
+def test_one_launch_for_few_tokens_leaves_what_the_three_kernels_leave(tokens, top, experts, identity):
+    from hymt2sharp_b200.kernels import ops
+    torch.manual_seed(tokens)
+    outputs = experts + identity
+    logits = (torch.randn(tokens, outputs) * 2).to(DEV)
+    corr = (torch.randn(outputs) * 0.2).to(DEV)
+    for kernel in ("skinny", "simt"):
+        tile = ops.gemm_group_tile(kernel)
+        tiles = ops.moe_tiles(tokens, top, experts, tile)
+        made = []
+        for fused in (False, True):
+            chosen = torch.full((tokens, top), -7, dtype=torch.int32, device=DEV)
+            weight = torch.full((tokens, top), -7.0, device=DEV)
+            pair_row = torch.full((tokens, top), -7, dtype=torch.int32, device=DEV)
+            row_token = torch.full((tiles * tile,), -7, dtype=torch.int32, device=DEV)
+            tile_group = torch.full((tiles + 1,), -7, dtype=torch.int32, device=DEV)
+            if fused:
+                ops.moe_route_place(chosen, weight, pair_row, row_token, tile_group, logits, corr, experts, tile)
+            else:
+                ops.moe_route(chosen, weight, logits, corr)
+                ops.moe_place(pair_row, row_token, tile_group, torch.zeros(max(experts, 1), dtype=torch.int32, device=DEV), chosen, experts, tile)
+            made.append([t.cpu() for t in (chosen, weight, pair_row, row_token, tile_group)])
+        for a, b in zip(*made):
+            assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_the_norm_behind_a_mixture_in_one_kernel(dtype):
+    """forward_then_norm against forward followed by the norm's own kernel, with and without a shared expert, with the rounded
+    rows asked for and not."""
+    from types import SimpleNamespace
+    from hymt2sharp_b200.parts import PartSpec, build_part
+    torch.manual_seed(1)
+    H = 72
+    norm = build_part("norm", PartSpec("rmsnorm", dict(dim=H, eps=1e-5, weight="n")))
+    for shared in (None, 40):
+        sh = None if shared is None else PartSpec("dense_mlp", dict(hidden=H, intermediate=shared, activation="relu2", up_proj="m.shared.up",
+                                                                    down_proj="m.shared.down"))
+        part = build_part("feed_forward", PartSpec("routed_experts", dict(hidden=H, experts=4, identity=2, top=3, intermediate=24, activation="relu2",
+                                                                          router="m.router", correction="m.correction", up_proj="m.e{}.up",
+                                                                          down_proj="m.e{}.down", shared=sh)))
+        w = {n: (torch.randn(s.shape) * 0.3).to(torch.bfloat16) for n, s in part.tensors().items()}
+        w["n"] = (1 + 0.1 * torch.randn(H)).to(torch.bfloat16)
+        part.load(w, DEV, dtype); norm.load(w, DEV, dtype)
+        for tokens in (3, 200):
+            x = torch.randn(tokens, H).to(torch.bfloat16).to(DEV).to(dtype)
+            start = torch.randn(tokens, H, device=DEV)
+            ctx = SimpleNamespace(norm_ahead=None, prenormed=None)
+            long_way, branch = start.clone(), torch.empty(tokens, H, device=DEV)
+            part.forward(x, branch, ctx, store=True)
+            norm.add_into(branch, long_way)
+            for want in (None, torch.bfloat16):
+                res = start.clone()
+                rows = part.forward_then_norm(x, res, norm, ctx, want)
+                helpers.assert_close(res.cpu().numpy(), long_way.cpu().numpy(), "float32", "one kernel against two", factor=2.0 if dtype == torch.float32 else 20.0)
+                assert (rows is None) == (want is None)
+                if rows is not None:
+                    assert torch.equal(rows, res.to(torch.bfloat16))
