@@ -71,8 +71,17 @@ moe_count_kernel(int* __restrict__ counts, const int* __restrict__ chosen, int p
     pdl_launch_dependents();
     const int e = blockIdx.x;
     int n = 0;
-    if (e < experts)   // (a mixture of identity experts only still runs one block, which finds nothing)
-        for (int i = threadIdx.x; i < pairs; i += blockDim.x) n += chosen[i] == e;
+    if (e < experts) {   // (a mixture of identity experts only still runs one block, which finds nothing)
+        // 16 bytes a load and four loads in flight: few blocks walk all pairs, and only their loads' latency costs
+        const int quads = ((uintptr_t)chosen % 16 == 0) ? pairs / 4 : 0;
+        const int4* c4 = reinterpret_cast<const int4*>(chosen);
+#pragma unroll 4
+        for (int i = threadIdx.x; i < quads; i += blockDim.x) {
+            const int4 v = __ldg(c4 + i);
+            n += (v.x == e) + (v.y == e) + (v.z == e) + (v.w == e);
+        }
+        for (int i = quads * 4 + threadIdx.x; i < pairs; i += blockDim.x) n += chosen[i] == e;
+    }
     // (counts of up to 2^24 are exact in float32)
     const float total = block_sum((float)n, scratch);
     if (threadIdx.x == 0) counts[e] = (int)total;
@@ -102,7 +111,8 @@ moe_place_kernel(int* __restrict__ pair_row, int* __restrict__ row_token, int* _
     for (int c0 = 0; c0 < pairs; c0 += PLACE_CHUNK) {
         const int n = min(PLACE_CHUNK, pairs - c0);
         __syncthreads();
-        for (int i = threadIdx.x; i < n; i += blockDim.x) chunk[i] = chosen[c0 + i];   // neighbours read neighbours
+#pragma unroll 8
+        for (int i = threadIdx.x; i < n; i += blockDim.x) chunk[i] = __ldg(chosen + c0 + i);   // neighbours read neighbours
         __syncthreads();
         // A thread owns a run of consecutive pairs: it counts its hits, a scan over the threads' counts gives the place of
         // its first hit, and a second walk over the run writes the rows.  Pairs keep their order.

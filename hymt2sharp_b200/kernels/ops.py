@@ -1370,7 +1370,7 @@ def attention_decode_kv(out: torch.Tensor, q: torch.Tensor, k_plane: torch.Tenso
                                             _ptr(counters), _stream()), "attention_decode")
 
 
-MOE_SMALL_PAIRS = 256   # up to this many (token, choice) pairs one block routes and sorts a step
+MOE_SMALL_PAIRS = 64   # up to this many (token, choice) pairs one block routes and sorts a step
 
 
 def moe_route_place(chosen: torch.Tensor, weight: torch.Tensor, pair_row: torch.Tensor, row_token: torch.Tensor, tile_group: torch.Tensor,

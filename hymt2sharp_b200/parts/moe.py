@@ -21,7 +21,9 @@ from .base import PartSpec, build_part, register_part
 from .linear import Linear, compute_form
 
 ACTIVATIONS = {"relu2": ops.EPILOGUE_RELU_SQUARED}
-SKINNY_MAX_PAIRS = 512   # up to this many (token, choice) pairs in a step the kernel for few rows runs the experts
+SKINNY_MAX_PAIRS = 512        # up to this many (token, choice) pairs in a step the kernel for few rows runs the experts,
+SKINNY_PAIRS_BESIDE_TC = 64   # where the tensor cores take the operands only up to this many: beyond, most experts meet several
+                              # rows, and a row tile of 128 on the tensor cores, mostly empty, still reads each expert once
 
 
 class RoutedExperts:
@@ -76,11 +78,11 @@ class RoutedExperts:
         what reading those experts' weights costs (the kernel for few rows); many pairs go to the tensor cores where the
         operands are bfloat16 with rows in whole 16-byte pieces; everything else to the general CUDA-core kernel."""
         same = self.up is not None and x.dtype == self.up.dtype
-        if same and tokens * self.top <= SKINNY_MAX_PAIRS:
+        pairs = tokens * self.top
+        tensor_cores = same and x.dtype == torch.bfloat16 and self.hidden % 8 == 0 and self.intermediate % 8 == 0
+        if same and pairs <= (SKINNY_PAIRS_BESIDE_TC if tensor_cores else SKINNY_MAX_PAIRS):
             return "skinny"
-        if same and x.dtype == torch.bfloat16 and self.hidden % 8 == 0 and self.intermediate % 8 == 0:
-            return "tc"
-        return "simt"
+        return "tc" if tensor_cores else "simt"
 
     def _experts(self, x: torch.Tensor, ctx):
         """Routing, the sorted rows and the experts' products: (y, pair_row, weight), y float32 [sorted rows, hidden]."""

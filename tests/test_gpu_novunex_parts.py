@@ -298,11 +298,11 @@ def test_sorted_rows_hold_every_pair_once_in_token_order(tokens, top, experts, i
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("hidden, experts, identity, top, ff, shared, tokens", [
     (42, 3, 2, 2, 11, 13, 70), (64, 8, 4, 3, 64, 128, 300), (40, 5, 0, 1, 8, None, 9), (48, 1, 3, 4, 5, 6, 1), (32, 0, 3, 2, 8, None, 20),
-    (42, 3, 2, 2, 11, 13, 400), (128, 6, 1, 2, 72, None, 700)])
+    (42, 3, 2, 2, 11, 13, 400), (128, 6, 1, 2, 72, None, 700), (64, 8, 4, 3, 64, 128, 30)])
 def test_mixture_of_experts_against_plain(dtype, hidden, experts, identity, top, ff, shared, tokens):
-    """Few (token, choice) pairs run the grouped product for few rows; many run the tensor-core one in bfloat16 where rows are
-    whole 16-byte pieces (the cases of 300 and 700 tokens) and the general one otherwise (400 tokens of 42 entries, and every
-    32-bit case with many pairs)."""
+    """Few (token, choice) pairs run the grouped product for few rows; more run the tensor-core one in bfloat16 where rows are
+    whole 16-byte pieces (the cases of 300 and 700 tokens, and 20 tokens of 64 entries) and the general one otherwise (400
+    tokens of 42 entries, and every 32-bit case with many pairs)."""
     from hymt2sharp_b200.parts import PartSpec, build_part
     torch.manual_seed(hidden + tokens)
     sh = None if shared is None else PartSpec("dense_mlp", dict(hidden=hidden, intermediate=shared, activation="relu2",
@@ -313,7 +313,8 @@ def test_mixture_of_experts_against_plain(dtype, hidden, experts, identity, top,
     w = {n: (torch.randn(s.shape) * 0.3).to(torch.bfloat16) for n, s in part.tensors().items()}
     w["m.router"] = (w["m.router"].float() * 4).to(torch.bfloat16)
     part.load(w, DEV, dtype)
-    want = "skinny" if tokens * top <= 512 else ("tc" if dtype == torch.bfloat16 and hidden % 8 == 0 else "simt")
+    tc = dtype == torch.bfloat16 and hidden % 8 == 0 and ff % 8 == 0
+    want = "skinny" if tokens * top <= (64 if tc else 512) else ("tc" if tc else "simt")
     assert experts == 0 or part._grouped_kernel(torch.empty(1, dtype=dtype, device=DEV), tokens) == want
     x = torch.randn(tokens, hidden).to(torch.bfloat16).float()
     mlp = dict(router=dict(experts=experts, identity=identity, top=top), expert=dict(ff=ff), shared=None if shared is None else dict(ff=shared))
@@ -396,7 +397,7 @@ def test_block_with_norms_behind_the_sublayers_only(dtype):
     helpers.assert_close(res.cpu().numpy(), r.numpy(), "float32" if dtype == torch.float32 else "bfloat16", "two blocks", factor=2.0)
 
 
-@pytest.mark.parametrize("tokens, top, experts, identity", [(1, 1, 1, 0), (5, 2, 3, 2), (64, 4, 32, 2), (20, 3, 0, 4), (9, 4, 1, 3)])
+@pytest.mark.parametrize("tokens, top, experts, identity", [(1, 1, 1, 0), (5, 2, 3, 2), (16, 4, 32, 2), (20, 3, 0, 4), (9, 4, 1, 3)])
 def test_one_launch_for_few_tokens_leaves_what_the_three_kernels_leave(tokens, top, experts, identity):
     from hymt2sharp_b200.kernels import ops
     torch.manual_seed(tokens)
