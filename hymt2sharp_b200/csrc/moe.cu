@@ -93,7 +93,7 @@ __global__ void __launch_bounds__(PLACE_THREADS)
 moe_place_kernel(int* __restrict__ pair_row, int* __restrict__ row_token, int* __restrict__ tile_group,
                  const int* __restrict__ counts, const int* __restrict__ chosen, int pairs, int top, int experts, int tile,
                  int max_tiles) {
-    __shared__ int chunk[PLACE_CHUNK];
+    __shared__ int chunk[PLACE_CHUNK + PLACE_CHUNK / 32];   // one word of padding every 32: a thread's run starts in a bank of its own
     __shared__ int warp_total[PLACE_THREADS / 32];
     __shared__ int base_s;
     pdl_wait();
@@ -112,7 +112,7 @@ moe_place_kernel(int* __restrict__ pair_row, int* __restrict__ row_token, int* _
         const int n = min(PLACE_CHUNK, pairs - c0);
         __syncthreads();
 #pragma unroll 8
-        for (int i = threadIdx.x; i < n; i += blockDim.x) chunk[i] = __ldg(chosen + c0 + i);   // neighbours read neighbours
+        for (int i = threadIdx.x; i < n; i += blockDim.x) chunk[i + (i >> 5)] = __ldg(chosen + c0 + i);   // neighbours read neighbours
         __syncthreads();
         // A thread owns a run of consecutive pairs: it counts its hits, a scan over the threads' counts gives the place of
         // its first hit, and a second walk over the run writes the rows.  Pairs keep their order.
@@ -120,7 +120,7 @@ moe_place_kernel(int* __restrict__ pair_row, int* __restrict__ row_token, int* _
         const int i0 = min(n, (int)threadIdx.x * run), i1 = min(n, i0 + run);
         int hits = 0;
         if (e < experts)
-            for (int i = i0; i < i1; i++) hits += chunk[i] == e;
+            for (int i = i0; i < i1; i++) hits += chunk[i + (i >> 5)] == e;
         int incl = hits;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
@@ -136,7 +136,7 @@ moe_place_kernel(int* __restrict__ pair_row, int* __restrict__ row_token, int* _
         }
         int at = base + placed + before;
         for (int i = i0; i < i1; i++) {
-            const int c = chunk[i];
+            const int c = chunk[i + (i >> 5)];
             if (c == e && e < experts) {
                 pair_row[c0 + i] = at;
                 row_token[at] = (c0 + i) / top;
