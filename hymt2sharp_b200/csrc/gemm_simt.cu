@@ -266,7 +266,7 @@ gemm_skinny_batched_kernel(TC* __restrict__ C, const T* __restrict__ A, const T*
 // The grouped product for few sorted rows (a decode step): row tiles of GROUP_SKINNY_ROWS rows, a warp per output column
 // reads its weight row once, 16 bytes a lane, and keeps a float32 sum for every row of the tile.  The time is that of
 // reading the matrices of the groups in use once.
-constexpr int GROUP_SKINNY_ROWS = 8;
+constexpr int GROUP_SKINNY_ROWS = 8, GROUP_SKINNY_COLS = 2;   // rows of a tile; output columns (weight rows) of a warp
 
 template <typename T, typename TC, int EPI>
 __global__ void __launch_bounds__(SKINNY_WARPS * 32)
@@ -277,8 +277,9 @@ gemm_skinny_grouped_kernel(TC* __restrict__ C, const T* __restrict__ A, const T*
     const int group = tile_group[blockIdx.y];
     if (group < 0) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n = blockIdx.x * SKINNY_WARPS + warp;
-    if (n >= N) return;
+    constexpr int COLS = GROUP_SKINNY_COLS;
+    const int n0 = (blockIdx.x * SKINNY_WARPS + warp) * COLS;
+    if (n0 >= N) return;
     const int m0 = blockIdx.y * GROUP_SKINNY_ROWS;
     const T* a_row[GROUP_SKINNY_ROWS];
     bool ok[GROUP_SKINNY_ROWS];
@@ -288,54 +289,76 @@ gemm_skinny_grouped_kernel(TC* __restrict__ C, const T* __restrict__ A, const T*
         ok[m] = src >= 0;
         a_row[m] = A + (size_t)(ok[m] ? (gather ? src : m0 + m) : 0) * lda;
     }
-    const T* w = W + (size_t)group * w_gs + (size_t)n * K;
-    float acc[GROUP_SKINNY_ROWS];
+    const T* w[COLS];
 #pragma unroll
-    for (int m = 0; m < GROUP_SKINNY_ROWS; m++) acc[m] = 0.f;
+    for (int c = 0; c < COLS; c++) w[c] = W + (size_t)group * w_gs + (size_t)(n0 + c < N ? n0 + c : n0) * K;
+    float acc[COLS][GROUP_SKINNY_ROWS];
+#pragma unroll
+    for (int c = 0; c < COLS; c++)
+#pragma unroll
+        for (int m = 0; m < GROUP_SKINNY_ROWS; m++) acc[c][m] = 0.f;
     constexpr int V = 16 / sizeof(T);
     if (vec) {
-        // four pieces of the weight row in flight per lane: the kernel's time is the weights' way from memory
+        // four pieces of each weight row in flight per lane: the kernel's time is the weights' way from memory
         constexpr int U = 4;
         for (int k0 = lane * V; k0 < K; k0 += 32 * V * U) {
-            uint4 raw[U];
+            uint4 raw[U][COLS];
 #pragma unroll
             for (int u = 0; u < U; u++) {
                 const int k = k0 + u * 32 * V;
-                raw[u] = k < K ? __ldg(reinterpret_cast<const uint4*>(w + k)) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+                for (int c = 0; c < COLS; c++)
+                    raw[u][c] = k < K ? __ldg(reinterpret_cast<const uint4*>(w[c] + k)) : make_uint4(0, 0, 0, 0);
             }
 #pragma unroll
             for (int u = 0; u < U; u++) {
                 const int k = k0 + u * 32 * V;
                 if (k >= K) break;
-                float wv[V];
-                const T* wt = reinterpret_cast<const T*>(&raw[u]);
+                float wv[COLS][V];
 #pragma unroll
-                for (int i = 0; i < V; i++) wv[i] = to_float(wt[i]);
+                for (int c = 0; c < COLS; c++) {
+                    const T* wt = reinterpret_cast<const T*>(&raw[u][c]);
+#pragma unroll
+                    for (int i = 0; i < V; i++) wv[c][i] = to_float(wt[i]);
+                }
 #pragma unroll
                 for (int m = 0; m < GROUP_SKINNY_ROWS; m++) {
                     if (ok[m]) {
                         const uint4 ra = *reinterpret_cast<const uint4*>(a_row[m] + k);
                         const T* at = reinterpret_cast<const T*>(&ra);
 #pragma unroll
-                        for (int i = 0; i < V; i++) acc[m] = fmaf(to_float(at[i]), wv[i], acc[m]);
+                        for (int i = 0; i < V; i++) {
+                            const float av = to_float(at[i]);
+#pragma unroll
+                            for (int c = 0; c < COLS; c++) acc[c][m] = fmaf(av, wv[c][i], acc[c][m]);
+                        }
                     }
                 }
             }
         }
     } else {
         for (int k = lane; k < K; k += 32) {
-            const float wv = to_float(w[k]);
+            float wv[COLS];
+#pragma unroll
+            for (int c = 0; c < COLS; c++) wv[c] = to_float(w[c][k]);
 #pragma unroll
             for (int m = 0; m < GROUP_SKINNY_ROWS; m++)
-                if (ok[m]) acc[m] = fmaf(to_float(a_row[m][k]), wv, acc[m]);
+                if (ok[m]) {
+                    const float av = to_float(a_row[m][k]);
+#pragma unroll
+                    for (int c = 0; c < COLS; c++) acc[c][m] = fmaf(av, wv[c], acc[c][m]);
+                }
         }
     }
 #pragma unroll
     for (int m = 0; m < GROUP_SKINNY_ROWS; m++) {
         if (ok[m]) {
-            float v = warp_sum(acc[m]);
-            if constexpr (EPI == EPI_RELU_SQUARED) { v = fmaxf(v, 0.f); v = v * v; }
-            if (lane == 0) C[(size_t)(m0 + m) * ldc + n] = from_float<TC>(v);
+#pragma unroll
+            for (int c = 0; c < COLS; c++) {
+                float v = warp_sum(acc[c][m]);
+                if constexpr (EPI == EPI_RELU_SQUARED) { v = fmaxf(v, 0.f); v = v * v; }
+                if (lane == 0 && n0 + c < N) C[(size_t)(m0 + m) * ldc + n0 + c] = from_float<TC>(v);
+            }
         }
     }
 }
@@ -421,7 +444,8 @@ HYMT2_API int hymt2_gemm_skinny_grouped(void* C, int c_dtype, const void* A, con
     HYMT2_REQUIRE(tiles > 0 && tiles <= 65535 && N > 0 && K > 0, "gemm_skinny_grouped: bad sizes tiles=%d N=%d K=%d", tiles, N, K);
     HYMT2_REQUIRE(epilogue == EPI_STORE || epilogue == EPI_RELU_SQUARED, "gemm_skinny_grouped: unknown epilogue %d", epilogue);
     HYMT2_REQUIRE(lda >= K && ldc >= N && tile_group && row_source, "gemm_skinny_grouped: bad arguments");
-    const dim3 grid((N + SKINNY_WARPS - 1) / SKINNY_WARPS, tiles);
+    const int per_block = SKINNY_WARPS * GROUP_SKINNY_COLS;
+    const dim3 grid((N + per_block - 1) / per_block, tiles);
     HYMT2_DISPATCH_DTYPE(dtype, T, {
         const long v = 16 / sizeof(T);
         const bool vec = K % v == 0 && lda % v == 0 && w_gs % v == 0 && (uintptr_t)A % 16 == 0 && (uintptr_t)W % 16 == 0;

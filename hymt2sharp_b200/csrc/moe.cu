@@ -257,22 +257,34 @@ moe_route_place_small_kernel(int* __restrict__ chosen, float* __restrict__ weigh
 
 // The mixture's last step and the norm behind the sublayer in one pass over a token's row:
 //   v = (branch[t] if given) + sum_k weight[t, k] * (y[pair_row[t, k]] or x[t]);  residual[t] += v / rms(v) * gain;  rows[t] = residual[t] rounded
+constexpr int COMBINE_MAX_TOP = 16;   // choices of a token whose rows and weights are held in shared memory
+
 template <typename TX, typename TW, typename TH>
 __global__ void __launch_bounds__(256)
 moe_combine_norm_kernel(float* __restrict__ residual, TH* __restrict__ rows, const float* __restrict__ branch, const float* __restrict__ y,
                         const TX* __restrict__ x, const int* __restrict__ pair_row, const float* __restrict__ weight,
                         const TW* __restrict__ gain, int width, int top, float eps) {
     extern __shared__ float smem[];   // [width] the row, then 33 floats for the block sum
+    __shared__ int row_s[COMBINE_MAX_TOP];
+    __shared__ float weight_s[COMBINE_MAX_TOP];
     pdl_wait();
     pdl_launch_dependents();
     const size_t t = blockIdx.x;
+    // the token's rows and weights once, so that the loads of the loop below depend on nothing but their index
+    const bool held = top <= COMBINE_MAX_TOP;
+    if (held && threadIdx.x < top) {
+        row_s[threadIdx.x] = pair_row[t * top + threadIdx.x];
+        weight_s[threadIdx.x] = weight[t * top + threadIdx.x];
+    }
+    __syncthreads();
     float ss = 0.f;
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
         float acc = branch ? branch[t * width + i] : 0.f;
+        const float own = to_float(x[t * width + i]);
         for (int k = 0; k < top; k++) {
-            const int row = pair_row[t * top + k];
-            const float v = row >= 0 ? y[(size_t)row * width + i] : to_float(x[t * width + i]);
-            acc = fmaf(weight[t * top + k], v, acc);
+            const int row = held ? row_s[k] : pair_row[t * top + k];
+            const float v = row >= 0 ? y[(size_t)row * width + i] : own;
+            acc = fmaf(held ? weight_s[k] : weight[t * top + k], v, acc);
         }
         smem[i] = acc;
         ss = fmaf(acc, acc, ss);

@@ -37,10 +37,10 @@ CONFIGS = {
     # sizes in multiples of 16 with heads of 64 and 128: the bfloat16 engine takes its tensor-core kernels where it has
     # them; 17 router outputs of which 4 are chosen; a kv_from layer right behind its source and one two layers on
     "even": dict(config=dict(architecture=ARCH, vocab=512, width=128, norm=dict(eps=1e-6), layers=[
-        _layer("attention_2", 8, 2, 64, 32, 0.125, 10000.0, 64, scaling=dict(factor=8.0, low=1.0, high=4.0, original=256),
+        _layer("attention_2", 8, 2, 64, 32, 0.125, 10000.0, 64, scaling=dict(factor=6.0, low=1.0, high=3.0, original=256),
                mlp=_moe(16, 1, 4, 64, shared=96)),
-        _layer("attention", 4, 1, 128, 64, 0.09, 50000.0, 32, mlp=_moe(4, 4, 3, 32, shared=64)),
-        _layer("attention_2", 8, 2, 64, 32, 0.125, 10000.0, 64, scaling=dict(factor=8.0, low=1.0, high=4.0, original=256),
+        _layer("attention", 4, 1, 128, 64, 0.09, 40000.0, 48, mlp=_moe(4, 3, 3, 32, shared=64)),
+        _layer("attention_2", 8, 2, 64, 32, 0.125, 10000.0, 64, scaling=dict(factor=6.0, low=1.0, high=3.0, original=256),
                kv_from=0, mlp=_moe(16, 1, 4, 64)),
         _layer("attention", 2, 2, 64, 128, 0.11, 5000.0, 64, mlp=_moe(2, 0, 2, 48, shared=32)),
     ]), seed=22, sigma=0.08, spaced_corrections=True),

@@ -69,7 +69,7 @@ SCALED = dict(factor=4.0, low=1.0, high=4.0, original=64)
     ("attention_2", 40, 4, 2, 6, 9, 6, SCALED),         # values wider than keys, the whole head rotated, scaled frequencies
     ("attention", 64, 4, 4, 16, 16, 0, None),           # no rotation at all, as many kv heads as heads
     ("attention_2", 96, 8, 2, 64, 32, 64, SCALED),
-    ("attention", 128, 4, 2, 128, 64, 32, None),         # from here on the bfloat16 engine runs its tensor-core prompt kernel and
+    ("attention", 128, 6, 3, 128, 64, 48, None),         # from here on the bfloat16 engine runs its tensor-core prompt kernel and
     ("attention_2", 128, 8, 2, 64, 64, 64, SCALED),      # its streaming decode kernel: keys and values of 64 and 128 in every pairing,
     ("attention", 64, 2, 1, 64, 128, 16, None),          # with and without the sink
     ("attention_2", 128, 4, 4, 128, 128, 128, None),
@@ -187,7 +187,7 @@ def test_one_far_key_is_found_in_prompts_and_in_decoding(dtype, sink, key_at, d,
     sequence in the same batch.  Heads of 16 and 24 run the general kernels; heads of 128 and 64 the fast ones in bfloat16."""
     length = 600
     for decode_from in (None, 590):
-        outs, vs = _planted(dtype, sink, d, dv, 2, 2, length, key_at, decode_from, second=70)
+        outs, vs = _planted(dtype, sink, d, dv, 3, 2, length, key_at, decode_from, second=70)
         for t in (length - 1, length - 5):
             got = outs[(0, t)]
             want = vs[0][key_at][:, None, :].expand_as(got)
@@ -297,11 +297,11 @@ def test_sorted_rows_hold_every_pair_once_in_token_order(tokens, top, experts, i
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("hidden, experts, identity, top, ff, shared, tokens", [
-    (42, 3, 2, 2, 11, 13, 70), (64, 8, 4, 3, 64, 128, 300), (40, 5, 0, 1, 8, None, 9), (48, 1, 3, 4, 5, 6, 1), (32, 0, 3, 2, 8, None, 20),
-    (42, 3, 2, 2, 11, 13, 400), (128, 6, 1, 2, 72, None, 700), (64, 8, 4, 3, 64, 128, 30)])
+    (42, 3, 2, 2, 11, 13, 70), (64, 6, 3, 2, 56, 120, 300), (40, 5, 0, 1, 8, None, 9), (48, 1, 3, 4, 5, 6, 1), (32, 0, 3, 2, 8, None, 20),
+    (42, 3, 2, 2, 11, 13, 400), (128, 6, 1, 2, 72, None, 700), (64, 6, 3, 2, 56, 120, 30)])
 def test_mixture_of_experts_against_plain(dtype, hidden, experts, identity, top, ff, shared, tokens):
     """Few (token, choice) pairs run the grouped product for few rows; more run the tensor-core one in bfloat16 where rows are
-    whole 16-byte pieces (the cases of 300 and 700 tokens, and 20 tokens of 64 entries) and the general one otherwise (400
+    whole 16-byte pieces (the cases of 300 and 700 tokens, and 30 tokens of 64 entries) and the general one otherwise (400
     tokens of 42 entries, and every 32-bit case with many pairs)."""
     from hymt2sharp_b200.parts import PartSpec, build_part
     torch.manual_seed(hidden + tokens)
