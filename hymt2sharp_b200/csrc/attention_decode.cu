@@ -181,20 +181,23 @@ attention_decode_kernel(DecodeParams p) {
 #pragma unroll
         for (int e = 0; e < EV; e++) acc[h][e] = 0.f;
     {
-        uint4 vraw[PF][EV / 8];
-        bool okv[PF];
+        // narrow values are one 16-byte piece a lane: twice as many of them in flight keep as many bytes on the way
+        constexpr int PFV = EV <= 8 ? 2 * PF : PF;
+        static_assert(ITERS % PFV == 0, "the ring of values in flight divides a warp's keys");
+        uint4 vraw[PFV][EV / 8];
+        bool okv[PFV];
 #pragma unroll
-        for (int i = 0; i < PF; i++) {
+        for (int i = 0; i < PFV; i++) {
             const size_t a = address_v(i, okv[i]);
             load_row<EV>(p.v_cache + a, vraw[i], okv[i]);
         }
 #pragma unroll
         for (int it = 0; it < ITERS; it++) {
-            const int st = it % PF;
+            const int st = it % PFV;
             float vf[EV];
             unpack<EV>(vraw[st], vf);
-            if (it + PF < ITERS) {
-                const size_t a = address_v(it + PF, okv[st]);
+            if (it + PFV < ITERS) {
+                const size_t a = address_v(it + PFV, okv[st]);
                 load_row<EV>(p.v_cache + a, vraw[st], okv[st]);
             }
             const float* pr = sm_p[warp][it * KEYS_PER_ITER + keygrp];   // 0 for keys that are not visible
